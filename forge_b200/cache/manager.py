@@ -22,6 +22,7 @@ class GroupSpec:
     name: str
     num_pages: int
     window: Optional[int] = None      # None: all positions are kept
+    keep_first: int = 0               # with a window: the first positions of a sequence stay readable for good
 
 
 @dataclass
@@ -115,7 +116,7 @@ class CacheManager:
     def release_out_of_window(self, req_id):
         """After a step: gives back the pages of windowed groups that no future query can read.  The next
         query is at position >= num_tokens and reads keys > position - window, so a page whose last
-        position is <= num_tokens - window is dead.  Returns the number of pages released."""
+        position is <= num_tokens - window is dead, unless it holds one of the group's kept first positions.  Returns the number of pages released."""
         r = self._requests[req_id]
         released = 0
         for g, spec in self.groups.items():
@@ -124,7 +125,8 @@ class CacheManager:
             table = r.tables[g]
             first_needed = r.num_tokens - spec.window + 1          # smallest key position a future query reads
             dead_pages = max(0, first_needed) // self.page_size     # pages wholly below it
-            for i in range(min(dead_pages, len(table))):
+            kept_pages = self._pages_for(spec.keep_first)           # pages that hold a position every query may read
+            for i in range(kept_pages, min(dead_pages, len(table))):
                 if table[i] >= 0:
                     self.pools[g].release(table[i], req_id)
                     table[i] = -1

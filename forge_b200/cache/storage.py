@@ -23,14 +23,15 @@ class LayerCache:
     storage, and whether it may write."""
     group: Optional[str]
     page_size: int
-    kv: Optional[torch.Tensor] = None          # [num_pages, 2, NKV, page_size, HD]
+    kv: Optional[torch.Tensor] = None          # [num_pages, 2, NKV, page_size, HD]; value heads of another size: [num_pages, row]
     state: Optional[torch.Tensor] = None       # [max_requests, *shape]
     writable: bool = True
 
 
 def group_name(spec: KVCacheSpec):
-    w = "full" if spec.window is None else f"win{spec.window}"
-    return f"kv{spec.num_kv_heads}x{spec.head_dim}_{w}"
+    w = "full" if spec.window is None else f"win{spec.window}" + (f"+first{spec.keep_first}" if spec.keep_first else "")
+    v = "" if spec.value_dim == spec.head_dim else f"v{spec.value_dim}"
+    return f"kv{spec.num_kv_heads}x{spec.head_dim}{v}_{w}"
 
 
 def plan_groups(cache_specs, cache_from):
@@ -44,7 +45,7 @@ def plan_groups(cache_specs, cache_from):
             if cache_from[src] is not None:
                 raise CacheError(f"layer {i} reads the cache of layer {src}, which has none of its own")
             if isinstance(spec, KVCacheSpec) and isinstance(s2, KVCacheSpec) and \
-                    (spec.num_kv_heads, spec.head_dim) != (s2.num_kv_heads, s2.head_dim):
+                    (spec.num_kv_heads, spec.head_dim, spec.value_dim) != (s2.num_kv_heads, s2.head_dim, s2.value_dim):
                 raise CacheError(f"layer {i} cannot read the cache of layer {src}: shapes differ")
             spec = s2
         if isinstance(spec, KVCacheSpec):
@@ -63,7 +64,7 @@ def bytes_per_page(cache_specs, cache_from, page_size, dtype):
     out = {g: 0 for g in groups}
     for i, spec in enumerate(cache_specs):
         if cache_from[i] is None and isinstance(spec, KVCacheSpec):
-            out[layer_group[i]] += 2 * spec.num_kv_heads * page_size * spec.head_dim * el
+            out[layer_group[i]] += spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim) * el
     return out
 
 
@@ -73,7 +74,7 @@ class CacheStorage:
         groups, self.layer_group = plan_groups(cache_specs, cache_from)
         if isinstance(pages_per_group, int):
             pages_per_group = {g: pages_per_group for g in groups}
-        self.manager = CacheManager([GroupSpec(g, pages_per_group[g], s.window) for g, s in groups.items()],
+        self.manager = CacheManager([GroupSpec(g, pages_per_group[g], s.window, s.keep_first) for g, s in groups.items()],
                                     page_size, max_requests)
         self.page_size, self.max_requests, self.dtype, self.device = page_size, max_requests, dtype, device
         self.layers = []
@@ -84,8 +85,9 @@ class CacheStorage:
                 self.layers.append(None)       # filled below
                 continue
             if isinstance(spec, KVCacheSpec):
-                kv = self._guarded_zeros(f"keys/values of run {i}", (pages_per_group[self.layer_group[i]], 2, spec.num_kv_heads,
-                                                                     page_size, spec.head_dim), dtype)
+                shape = (2, spec.num_kv_heads, page_size, spec.head_dim) if spec.value_dim == spec.head_dim else \
+                    (spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim),)
+                kv = self._guarded_zeros(f"keys/values of run {i}", (pages_per_group[self.layer_group[i]], *shape), dtype)
                 self.layers.append(LayerCache(self.layer_group[i], page_size, kv=kv))
             elif isinstance(spec, StateSpec):
                 st = self._guarded_zeros(f"state of run {i}", (max_requests, *spec.shape), spec.dtype)
@@ -120,6 +122,14 @@ class CacheStorage:
                 if not bool((edge.view(torch.uint8) == self.CANARY_BYTE).all()):
                     bad.append(f"{what} (the guard {name} it)")
         return bad
+
+    def snapshot_state(self):
+        """Copies of every fixed-size state tensor (for a caller that has to run a step twice)."""
+        return [st.clone() for st in self._state_tensors]
+
+    def restore_state(self, kept):
+        for st, old in zip(self._state_tensors, kept):
+            st.copy_(old)
 
     def zero_state_slots(self, slots):
         """Clears the state rows of newly admitted requests."""

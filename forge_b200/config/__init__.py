@@ -1,5 +1,6 @@
 from .base import ConfigError, LayerSpec, ModelPlan, PartSpec
 from .llama import LlamaConfig
+from .zatupel import ZatupelConfig
 from .registry import (config_from_dict, load_config, register_architecture, registered_architectures,
                        unregister_architecture)
 
@@ -8,5 +9,8 @@ from .registry import (config_from_dict, load_config, register_architecture, reg
 register_architecture("LlamaForCausalLM", LlamaConfig, replace=True)
 register_architecture("Qwen2ForCausalLM", LlamaConfig, replace=True)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
+# a hybrid of windowed attention and two state-keeping mixers; its files name it with one string, "architecture"
+register_architecture("Zatupel", ZatupelConfig, replace=True)
+
+__all__ = ["ZatupelConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture"]

@@ -32,8 +32,10 @@ def registered_architectures():
 
 def config_from_dict(d):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):      # some designs name themselves with one string
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"no model registered for architecture {name!r}; known: {registered_architectures()}")

@@ -1,23 +1,26 @@
 // SwiGLU gate:  out[t,j] = silu(g) * u with g = gu[t,2j], u = gu[t,2j+1], silu(g) = g / (1 + expf(-g))
 // (formula of src/operators/cuda/cuda_elementwise.cu:34-41).  The gate and up projections are stored
 // with their rows interleaved, so one GEMM yields [T, 2I] with each (gate, up) pair adjacent.
+// act 1: the gate's activation is gelu_tanh(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) instead.
 #include "common.cuh"
 
 namespace {
 
 template <typename TOut>
-__global__ void silu_mul_interleaved_kernel(const float* __restrict__ gu, TOut* __restrict__ out, size_t n) {
+__global__ void silu_mul_interleaved_kernel(const float* __restrict__ gu, TOut* __restrict__ out, size_t n, int act) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float2 p = reinterpret_cast<const float2*>(gu)[i];
-    out[i] = forge::from_float<TOut>(p.x / (1.0f + expf(-p.x)) * p.y);
+    const float g = act == 1 ? 0.5f * p.x * (1.0f + tanhf(0.7978845608028654f * (p.x + 0.044715f * p.x * p.x * p.x)))
+                             : p.x / (1.0f + expf(-p.x));
+    out[i] = forge::from_float<TOut>(g * p.y);
 }
 
 }  // namespace
 
-extern "C" int forge_silu_mul_interleaved(const float* gu, void* out, int out_dtype, int T, int I,
+extern "C" int forge_silu_mul_interleaved(const float* gu, void* out, int out_dtype, int T, int I, int act,
                                           cudaStream_t stream) {
     if (T < 0 || I <= 0) return forge::fail(FORGE_ERR_ARG, "silu_mul: bad sizes T=%d I=%d", T, I);
     const size_t n = (size_t)T * I;
@@ -25,6 +28,6 @@ extern "C" int forge_silu_mul_interleaved(const float* gu, void* out, int out_dt
     const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(out_dtype, TO,
-        e = forge::launch(silu_mul_interleaved_kernel<TO>, dim3(blocks), dim3(256), 0, stream, 1, gu, (TO*)out, n));
+        e = forge::launch(silu_mul_interleaved_kernel<TO>, dim3(blocks), dim3(256), 0, stream, 1, gu, (TO*)out, n, act));
     return forge::check_launch("silu_mul_interleaved", e);
 }

@@ -18,6 +18,7 @@
 //   1  C fp32 += acc + bias                      (the residual stream)
 //   2  C bf16  = acc + bias
 //   3  C bf16[M, N/2]: out[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]     (gate/up rows interleaved in W)
+//   5  the same with gelu_tanh(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) as the gate's activation
 // Replaces the reference's cuBLAS GemmEx / tiled GEMM / GEMV trio and its separate bias-add, residual-add
 // and silu-multiply launches (src/operators/cuda/cuda_quant.cu:582-599, cuda_gemm.cu:7-55,
 // cuda_elementwise.cu:8-48).
@@ -33,7 +34,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kSmemLimit = 227 * 1024;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACCUM_F32 = 1, EPI_STORE_BF16 = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_ROPE = 4 };
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACCUM_F32 = 1, EPI_STORE_BF16 = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_ROPE = 4, EPI_GEGLU_BF16 = 5 };
 
 struct GemmParams {
     void* C;
@@ -60,6 +61,10 @@ template <int BN> struct Cfg {
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+__device__ __forceinline__ float gelu_tanh(float g) { return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))); }
+// the gate's activation of the two gated epilogues
+__device__ __forceinline__ bool is_gated(int epilogue) { return epilogue == EPI_SWIGLU_BF16 || epilogue == EPI_GEGLU_BF16; }
+__device__ __forceinline__ float gate_act(int epilogue, float g) { return epilogue == EPI_GEGLU_BF16 ? gelu_tanh(g) : silu(g); }
 
 // Applies the epilogue to 32 consecutive columns (n .. n+31) of output row m held in r (fp32 bits) and stores them.
 template <int BN>
@@ -106,7 +111,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
 #pragma unroll
                 for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(v[i]);
             }
-        } else {   // EPI_SWIGLU_BF16: N is even, pairs never straddle a 32-column chunk
+        } else {   // EPI_SWIGLU_BF16, EPI_GEGLU_BF16: N is even, pairs never straddle a 32-column chunk
             const int half_n = p.N >> 1;
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * half_n + (n >> 1);
             if (width == 32 && (half_n & 7) == 0) {
@@ -116,7 +121,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int q = 2 * (i + 2 * j);
-                        __nv_bfloat162 h = __floats2bfloat162_rn(silu(v[q]) * v[q + 1], silu(v[q + 2]) * v[q + 3]);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(gate_act(p.epilogue, v[q]) * v[q + 1], gate_act(p.epilogue, v[q + 2]) * v[q + 3]);
                         w4[j] = *reinterpret_cast<uint32_t*>(&h);
                     }
                     *reinterpret_cast<uint4*>(dst + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -124,7 +129,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(silu(v[2 * i]) * v[2 * i + 1]);
+                    if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(gate_act(p.epilogue, v[2 * i]) * v[2 * i + 1]);
             }
         }
     }
@@ -1103,11 +1108,11 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                         const int m = c + i;
                         if (m >= p.M) break;                       // uniform over the warp
                         const float v = __uint_as_float(r[i]) + b;
-                        if (p.epilogue == EPI_SWIGLU_BF16) {
+                        if (is_gated(p.epilogue)) {
                             const float other = __shfl_xor_sync(0xffffffffu, v, 1);
                             if ((lane & 1) == 0 && n + 1 < p.N)
                                 reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] =
-                                    __float2bfloat16_rn(silu(v) * other);
+                                    __float2bfloat16_rn(gate_act(p.epilogue, v) * other);
                         } else if (n < p.N) {
                             if (p.epilogue == EPI_STORE_BF16) {
                                 reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
@@ -1160,10 +1165,10 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
                 for (int i = 0; i < 4; ++i) if (n + i < p.N) v[i] += p.bias[n + i];
             }
-            if (p.epilogue == EPI_SWIGLU_BF16) {
+            if (is_gated(p.epilogue)) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * (p.N >> 1) + (n >> 1);
-                if (n + 1 < p.N) dst[0] = __float2bfloat16_rn(silu(v[0]) * v[1]);
-                if (n + 3 < p.N) dst[1] = __float2bfloat16_rn(silu(v[2]) * v[3]);
+                if (n + 1 < p.N) dst[0] = __float2bfloat16_rn(gate_act(p.epilogue, v[0]) * v[1]);
+                if (n + 3 < p.N) dst[1] = __float2bfloat16_rn(gate_act(p.epilogue, v[2]) * v[3]);
             } else if (p.epilogue == EPI_STORE_BF16) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
 #pragma unroll
@@ -1379,11 +1384,11 @@ gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             for (int m = 0; m < NT; ++m) {
                 if (m >= p.M) break;
                 const float v = acc[m] + b;
-                if (p.epilogue == EPI_SWIGLU_BF16) {
+                if (is_gated(p.epilogue)) {
                     const float other = __shfl_xor_sync(0xffffffffu, v, 1);
                     if ((lane & 1) == 0 && n + 1 < p.N)
                         reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] =
-                            __float2bfloat16_rn(silu(v) * other);
+                            __float2bfloat16_rn(gate_act(p.epilogue, v) * other);
                 } else if (n < p.N) {
                     if (p.epilogue == EPI_STORE_BF16) {
                         reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
@@ -1741,8 +1746,8 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     if (M < 0 || N <= 0 || K <= 0) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return FORGE_OK;
     if (K % 8 != 0) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: K=%d is not a multiple of 8 (TMA row stride)", K);
-    if (epilogue < 0 || epilogue > 3) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: unknown epilogue %d", epilogue);
-    if (epilogue == EPI_SWIGLU_BF16 && (N & 1)) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: swiglu epilogue needs even N, got %d", N);
+    if (epilogue < 0 || epilogue == EPI_QKV_ROPE || epilogue > EPI_GEGLU_BF16) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: unknown epilogue %d", epilogue);
+    if ((epilogue == EPI_SWIGLU_BF16 || epilogue == EPI_GEGLU_BF16) && (N & 1)) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: a gated epilogue needs even N, got %d", N);
     if (g_num_sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);

@@ -1,0 +1,262 @@
+// Mixers that carry a matrix of state per head from token to token, and the small steps around them.
+//
+// A head has K key channels and K value channels; its state S is [K, K] (key channel x value channel) in fp32,
+// one per request slot, and everything that enters the recurrence is fp32.  Two recurrences:
+//
+//   decay-and-bonus ("wkv"):   o_t = (S + diag(u) k_t v_t^T)^T r_t ;   S <- diag(w_t) S + k_t v_t^T
+//                              w_t = exp(-exp(x_t + w0))
+//   generalized delta rule:    S <- diag(w_t) S - (a_t * n_t) (n_t^T S) + k_t v_t^T ;   o_t = S^T r_t
+//                              n_t = k_t / sqrt(|k_t|^2 + 1e-6),  w_t = exp(-exp(-1/2) sigmoid(x_t + w0)),
+//                              a_t = sigmoid(y_t + a0)               (both terms read the state before the step)
+//
+// One CTA per (request, head) walks the request's tokens of the step in order; thread j owns column j of S
+// (the K numbers that meet value channel j) in registers, so a token costs K multiply-adds per thread and no
+// exchange between threads except the vectors r, k, w (, a) of the token, which are staged in shared memory a few
+// tokens at a time.  The walk is the same whether a request's tokens come in one step or in many: state and sums
+// see the same operations in the same order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kScanTokens = 8;        // tokens whose vectors are staged at a time
+
+struct ScanInput {                    // a [T, heads * K] fp32 matrix that may be a column slice of a wider one
+    const float* p;
+    int ld;
+};
+
+__device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// MODE 0: decay and bonus; MODE 1: generalized delta rule.
+// x: what the decay is made from (before w0 is added); y: what the removal rate is made from (MODE 1).
+// last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the request's last row is
+// kept as fp32 at state + prev_off (the next step's "previous token").
+template <int KMAX, int MODE, typename TA>
+__global__ void __launch_bounds__(KMAX)
+state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y, const float* __restrict__ w0,
+                  const float* __restrict__ a0, const float* __restrict__ bonus, float* __restrict__ state, long long state_stride,
+                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, float* __restrict__ out,
+                  const TA* __restrict__ last_in, int W, long long prev_off, int N, int K) {
+    __shared__ float rs[kScanTokens][KMAX], ks[kScanTokens][KMAX], ds[kScanTokens][KMAX], as[MODE == 1 ? kScanTokens : 1][KMAX];
+    __shared__ float us[KMAX], vs[kScanTokens][KMAX];
+    forge::pdl_launch_dependents();
+    const int s = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
+    const bool live = j < K;
+    const int col = head * K + j;
+    const float w0j = live ? w0[col] : 0.f;
+    const float a0j = (MODE == 1 && live) ? a0[col] : 0.f;
+    if (MODE == 0) us[j] = live ? bonus[col] : 0.f;
+    forge::pdl_wait();
+    const int t_lo = q_start[s], t_hi = q_start[s + 1];
+    float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * K;
+    float S[KMAX];
+#pragma unroll
+    for (int i = 0; i < KMAX; ++i) S[i] = (live && i < K) ? S_g[(size_t)i * K + j] : 0.f;
+
+    for (int tb = t_lo; tb < t_hi; tb += kScanTokens) {
+        const int n = min(kScanTokens, t_hi - tb);
+        __syncthreads();                                   // the tokens before are done with the staged vectors
+#pragma unroll
+        for (int tt = 0; tt < kScanTokens; ++tt) {
+            float rj = 0.f, kj = 0.f, dj = 0.f, aj = 0.f, vj = 0.f;
+            if (tt < n && live) {
+                const size_t t = (size_t)(tb + tt);
+                rj = r.p[t * r.ld + col];
+                kj = k.p[t * k.ld + col];
+                vj = v.p[t * v.ld + col];
+                const float xj = x.p[t * x.ld + col] + w0j;
+                if (MODE == 0) dj = expf(-expf(xj));
+                else {
+                    dj = expf(-0.6065306597126334f * sigmoidf(xj));
+                    aj = sigmoidf(y.p[t * y.ld + col] + a0j);
+                }
+            }
+            rs[tt][j] = rj;
+            ks[tt][j] = kj;
+            ds[tt][j] = dj;
+            if (MODE == 1) as[tt][j] = aj;
+            vs[tt][j] = vj;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = vs[tt][j];
+            float acc = 0.f;
+            if (MODE == 0) {
+#pragma unroll
+                for (int i = 0; i < KMAX; ++i) {
+                    const float kv = ks[tt][i] * vj;
+                    acc = fmaf(rs[tt][i], fmaf(us[i], kv, S[i]), acc);
+                    S[i] = fmaf(ds[tt][i], S[i], kv);
+                }
+            } else {
+                float held = 0.f, kk = 0.f;                // k^T S (this column) and |k|^2
+#pragma unroll
+                for (int i = 0; i < KMAX; ++i) {
+                    held = fmaf(ks[tt][i], S[i], held);
+                    kk = fmaf(ks[tt][i], ks[tt][i], kk);
+                }
+                // (a * n)(n^T S) = a_i k_i (k^T S) / (|k|^2 + 1e-6): the two roots of the unit key multiply out
+                const float share = held / (kk + 1e-6f);
+#pragma unroll
+                for (int i = 0; i < KMAX; ++i) {
+                    S[i] = fmaf(ds[tt][i], S[i], ks[tt][i] * (vj - as[tt][i] * share));
+                    acc = fmaf(rs[tt][i], S[i], acc);
+                }
+            }
+            if (live) out[(size_t)(tb + tt) * N * K + col] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < KMAX; ++i)
+            if (i < K) S_g[(size_t)i * K + j] = S[i];
+    }
+    if (MODE == 0 && last_in != nullptr && t_hi > t_lo) {
+        float* prev = state + (size_t)slots[s] * state_stride + prev_off;
+        const TA* row = last_in + (size_t)(t_hi - 1) * W;
+        for (int c = head * KMAX + j; c < W; c += N * KMAX) prev[c] = forge::to_float(row[c]);
+    }
+}
+
+// The shifted inputs of a mixer that looks one token back: out[m][t][c] = h[t][c] + (prev[t][c] - h[t][c]) * mu[m][c],
+// prev = h[t-1] inside a request's tokens of the step, the kept row of the request's state for its first token.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+token_shift_kernel(const TA* __restrict__ h, const float* __restrict__ state, long long state_stride, long long prev_off,
+                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots,
+                   const float* __restrict__ mu, TA* __restrict__ out, int T, int W, int n_mix) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int t = blockIdx.x, s = tok_req[t];
+    const bool first = t == q_start[s];
+    const float* kept = state + (size_t)slots[s] * state_stride + prev_off;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float cur = forge::to_float(h[(size_t)t * W + c]);
+        const float prev = first ? kept[c] : forge::to_float(h[(size_t)(t - 1) * W + c]);
+        for (int m = 0; m < n_mix; ++m)
+            out[((size_t)m * T + t) * W + c] = forge::from_float<TA>(fmaf(prev - cur, mu[(size_t)m * W + c], cur));
+    }
+}
+
+// One warp per (token, head): the head's K outputs divided by their root mean square, times a weight per channel,
+// times a gate (act 0: sigmoid(g), 1: g * sigmoid(g)), stored in the activation type for the output projection.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+head_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight, ScanInput g, TA* __restrict__ out, int rows,
+                   int N, int K, float eps, int act) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= rows * N) return;
+    const int t = w / N, head = w % N;
+    const float* src = o + (size_t)t * N * K + head * K;
+    float ss = 0.f;
+    for (int c = lane; c < K; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = forge::warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)K + eps);
+    for (int c = lane; c < K; c += 32) {
+        const float gv = g.p[(size_t)t * g.ld + head * K + c];
+        const float gate = act == 1 ? gv * sigmoidf(gv) : sigmoidf(gv);
+        out[(size_t)t * N * K + head * K + c] = forge::from_float<TA>(src[c] * inv * weight[head * K + c] * gate);
+    }
+}
+
+// out[t][c] = tanh(in[t][c]) in the activation type (the hidden layer of a low-rank projection).
+template <typename TA>
+__global__ void tanh_rows_kernel(ScanInput in, TA* __restrict__ out, int T, int n) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * n) return;
+    out[i] = forge::from_float<TA>(tanhf(in.p[(i / n) * in.ld + i % n]));
+}
+
+template <int MODE, typename TA>
+cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y,
+                        const float* w0, const float* a0, const float* bonus, float* state, long long stride, const int32_t* q_start,
+                        const int32_t* slots, float* out, const TA* last_in, int W, long long prev_off, int N, int K) {
+#define FORGE_SCAN_CASE(KM)                                                                                              \
+    case KM:                                                                                                             \
+        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(KM), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
+                             state, stride, q_start, slots, out, last_in, W, prev_off, N, K);
+    switch (kmax) {
+        FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
+        default: return cudaErrorInvalidValue;
+    }
+#undef FORGE_SCAN_CASE
+}
+
+}  // namespace
+
+// mode 0 (decay and bonus) / 1 (generalized delta rule).  r, k, v, x (and y, mode 1): fp32, row t at p + t * ld, head n's
+// channels at columns n*K .. n*K+K-1.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  state: fp32 rows of state_stride
+// numbers, row slots[s] holds request s's N matrices [K, K] from its start.  out fp32 [T, N*K].  last_in (mode 0, optional):
+// the mixer's input [T, W] of type last_dtype, whose last row per request is kept at state + prev_off.
+extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float* k, int ld_k, const float* v, int ld_v,
+                                const float* x, int ld_x, const float* y, int ld_y, const float* w0, const float* a0,
+                                const float* bonus, float* state, long long state_stride, const int32_t* q_start,
+                                const int32_t* slots, float* out, const void* last_in, int last_dtype, int W, long long prev_off,
+                                int S, int N, int K, cudaStream_t stream) {
+    if (S < 0 || N <= 0 || K <= 0 || (mode != 0 && mode != 1))
+        return forge::fail(FORGE_ERR_ARG, "state_scan: bad sizes S=%d N=%d K=%d mode=%d", S, N, K, mode);
+    if (K > 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "state_scan: heads of %d channels (at most 128)", K);
+    if (state_stride < (long long)N * K * K) return forge::fail(FORGE_ERR_ARG, "state_scan: state rows are too short");
+    if (mode == 0 && !bonus) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 0 needs the bonus");
+    if (mode == 1 && (!y || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs the removal rate");
+    if (S == 0) return FORGE_OK;
+    const int kmax = (K + 31) / 32 * 32;
+    const dim3 grid(S, N);
+    ScanInput R{r, ld_r}, Kk{k, ld_k}, V{v, ld_v}, X{x, ld_x}, Y{y, ld_y};
+    cudaError_t e;
+    if (mode == 1) {
+        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, w0, a0, nullptr, state, state_stride, q_start, slots, out,
+                                  nullptr, 0, 0, N, K);
+    } else if (last_in == nullptr || last_dtype == FORGE_F32) {
+        e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, w0, nullptr, bonus, state, state_stride, q_start, slots, out,
+                                  (const float*)last_in, W, prev_off, N, K);
+    } else {
+        e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, w0, nullptr, bonus, state, state_stride, q_start, slots,
+                                          out, (const __nv_bfloat16*)last_in, W, prev_off, N, K);
+    }
+    return forge::check_launch("state_scan", e);
+}
+
+// h, out of type dtype: [T, W] and [n_mix, T, W]; mu fp32 [n_mix, W]; the kept row of request s: state + slots[s] * stride + prev_off.
+extern "C" int forge_token_shift(const void* h, const float* state, long long state_stride, long long prev_off, const int32_t* tok_req,
+                                 const int32_t* q_start, const int32_t* slots, const float* mu, void* out, int dtype, int T, int W,
+                                 int n_mix, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || n_mix <= 0) return forge::fail(FORGE_ERR_ARG, "token_shift: bad sizes T=%d W=%d n=%d", T, W, n_mix);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(token_shift_kernel<TT>, dim3(T), dim3(128), 0, stream, 1, (const TT*)h, state, state_stride, prev_off, tok_req,
+                          q_start, slots, mu, (TT*)out, T, W, n_mix));
+    return forge::check_launch("token_shift", e);
+}
+
+// o fp32 [T, N*K]; weight fp32 [N*K]; g fp32 rows of ld_g (the gate before its activation); out of type dtype [T, N*K].
+extern "C" int forge_head_finish(const float* o, const float* weight, const float* g, int ld_g, void* out, int dtype, int T, int N,
+                                 int K, float eps, int act, cudaStream_t stream) {
+    if (T < 0 || N <= 0 || K <= 0 || (act != 0 && act != 1)) return forge::fail(FORGE_ERR_ARG, "head_finish: bad sizes T=%d N=%d K=%d", T, N, K);
+    if (T == 0) return FORGE_OK;
+    if ((long long)T * N > 0x7fffffffLL / 2) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_finish: too many rows");
+    const unsigned blocks = (unsigned)(((long long)T * N + 3) / 4);
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(head_finish_kernel<TT>, dim3(blocks), dim3(128), 0, stream, 1, o, weight, ScanInput{g, ld_g}, (TT*)out, T, N, K,
+                          eps, act));
+    return forge::check_launch("head_finish", e);
+}
+
+extern "C" int forge_tanh_rows(const float* in, int ld, void* out, int dtype, int T, int n, cudaStream_t stream) {
+    if (T < 0 || n <= 0 || ld < n) return forge::fail(FORGE_ERR_ARG, "tanh_rows: bad sizes T=%d n=%d ld=%d", T, n, ld);
+    if (T == 0) return FORGE_OK;
+    const unsigned blocks = (unsigned)(((size_t)T * n + 255) / 256);
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(tanh_rows_kernel<TT>, dim3(blocks), dim3(256), 0, stream, 1, ScanInput{in, ld}, (TT*)out, T, n));
+    return forge::check_launch("tanh_rows", e);
+}
+
+extern "C" const char* forge_last_error() { return forge::error_buffer(); }

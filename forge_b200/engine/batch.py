@@ -45,6 +45,8 @@ class StepBatch:
     host_context_before: List[int] = field(default_factory=list)
     host_slots: List[int] = field(default_factory=list)
     attention_plan: dict = field(default_factory=dict)
+    # what one layer of the step leaves for later layers of the same step (device tensors that live as long as the step)
+    shared: dict = field(default_factory=dict)
 
 
 @dataclass

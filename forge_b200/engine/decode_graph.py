@@ -101,9 +101,13 @@ class DecodeGraph:
         device)."""
         self._fill(hs, tokens_from)
         if self.graph is None:
-            # first use: once eagerly (sets kernel attributes, warms allocator), then capture
+            # first use: once eagerly (sets kernel attributes, warms allocator), then capture.  The replay below runs
+            # the same step once more: writes into the pages are the same both times, but a mixer's fixed-size state
+            # would move twice, so it is put back as it was
             n0 = kernels.launch_count()
+            kept = self.runner.storage.snapshot_state()
             self._forward()
+            self.runner.storage.restore_state(kept)
             self.kernels_per_replay = kernels.launch_count() - n0
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()

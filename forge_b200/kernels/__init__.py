@@ -28,15 +28,15 @@ def dtype_code(dt):
     raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dt}")
 
 
-_P, _I, _F = c_void_p, c_int, c_float
+_P, _I, _F, _LL = c_void_p, c_int, c_float, ctypes.c_longlong
 
 _SIGNATURES = {
     "core": {
-        "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+        "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "forge_rope_table": [_P, _P, _I, _I, _F, _I, _P],
-        "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _P],
+        "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _I, _P],
         "forge_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_paged_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
         "forge_argmax": [_P, _P, _I, _I, _P],
@@ -58,6 +58,14 @@ _SIGNATURES = {
     "attention_sm100": {
         "forge_paged_attention_sm100": [_P] * 10 + [_I] + [_P] * 3 + [_I] * 9 + [_F, _P],
     },
+    "mixers": {
+        "forge_headmix_prepare": [_P, _I] + [_P] * 9 + [_I] * 8 + [_LL, _I, _P],
+        "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
+        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _P],
+        "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
+        "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
+    },
     "decode_layers": {
         "forge_decode_layers_desc_bytes": [],
         "forge_decode_layers_supports": [_I] * 6,
@@ -73,6 +81,7 @@ _libs = {}
 # tested before use, a bad one raises bit 4 of the step's status word and is skipped.  The entries that tell a
 # library the bounds, per library (one per source file that checks):
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
+                  "mixers": ["forge_checks_configure_attention_headmix"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -490,14 +499,14 @@ def new_ints(values, device):
 
 # ---------------------------------------------------------------------------------------------- core
 
-def embedding(ids, table, out=None, status=None):
-    """out[t,:] = table[ids[t],:] as float32 [T,H]; ids int32 [T]; table [V,H] float32 or bfloat16."""
+def embedding(ids, table, out=None, status=None, scale=1.0):
+    """out[t,:] = table[ids[t],:] * scale as float32 [T,H]; ids int32 [T]; table [V,H] float32 or bfloat16."""
     lib = library("core")
     T, (V, H) = ids.numel(), table.shape
     if out is None:
         out = new_tensor((T, H), torch.float32, table.device)
     _check(lib, lib.forge_embedding(_need(ids, "ids", torch.int32), _need(table, "table", ndim=2),
-                                    dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V,
+                                    dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V, float(scale),
                                     _opt(status, "status", torch.int32), _stream()), "embedding")
     return out
 
@@ -556,14 +565,18 @@ def rope_kv_write(qkv, positions, slot_mapping, kv_cache, n_heads, n_kv_heads, h
     return q_out
 
 
-def silu_mul_interleaved(gu, out_dtype, out=None):
-    """out[t,j] = silu(gu[t,2j]) * gu[t,2j+1]; gu float32 [T,2I]."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_mul_interleaved(gu, out_dtype, out=None, activation="silu"):
+    """out[t,j] = act(gu[t,2j]) * gu[t,2j+1]; gu float32 [T,2I]; act: silu, or the tanh form of gelu."""
     lib = library("core")
     T, two_i = gu.shape
     if out is None:
         out = new_tensor((T, two_i // 2), out_dtype, gu.device)
     _check(lib, lib.forge_silu_mul_interleaved(_need(gu, "gu", torch.float32, 2), _need(out, "out", out_dtype),
-                                               dtype_code(out_dtype), T, two_i // 2, _stream()), "silu_mul_interleaved")
+                                               dtype_code(out_dtype), T, two_i // 2, GATE_ACTIVATIONS[activation], _stream()),
+           "silu_mul_interleaved")
     return out
 
 
@@ -654,6 +667,167 @@ def sample(logits, temperature, top_k, top_p, u, out=None):
     _check(lib, lib.forge_sample(_need(logits, "logits", torch.float32, 2), _need(temperature, "temperature", torch.float32),
                                  _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32),
                                  _need(u, "u", torch.float32), _need(out, "out", torch.int32), R, V, _stream()), "sample")
+    return out
+
+
+# ------------------------------------------------------------------------------------------- mixers
+# Attention whose heads exchange their weights (csrc/attention_headmix.cu) and mixers with a matrix of state per head
+# (csrc/recurrent.cu).  Arithmetic is fp32 in both runtimes; the activation type is only what is stored.
+
+HEADMIX_SMEM_LIMIT = 200 * 1024
+
+
+def headmix_smem_bytes(H, G, D, E, TQ, KT):
+    return 4 * (TQ * H * (D + E) + G * KT * (D + 1 + E) + 2 * TQ * H * KT + 2 * TQ * H + H * H)
+
+
+def headmix_tile_shape(H, G, D, E, single_tokens=False):
+    """(tokens per tile, keys per chunk) of the attention kernel for these head counts and sizes: the largest that fit
+    the CTA's shared memory.  ``single_tokens``: a step of one token per request."""
+    for KT in (64, 32, 16, 8, 4, 2, 1):
+        for TQ in ((1,) if single_tokens else (16, 8, 4, 2, 1)):
+            if headmix_smem_bytes(H, G, D, E, TQ, KT) <= HEADMIX_SMEM_LIMIT:
+                return TQ, KT
+    raise KernelError(f"headmix attention: {H} heads of {D}/{E} channels do not fit a CTA's shared memory")
+
+
+def headmix_plan(batch, TQ, device):
+    """The step's tokens cut into tiles of up to TQ consecutive tokens of one request (first token, count), made once
+    per step.  A step of single tokens that a CUDA graph replays has no list: tile i is token i."""
+    if getattr(batch, "decode_only", False):
+        return None, None, batch.num_tokens
+    key = ("headmix", TQ)
+    plan = batch.attention_plan.get(key)
+    if plan is None:
+        t0, n, qs = [], [], batch.host_q_start
+        for s in range(batch.num_requests):
+            for a in range(qs[s], qs[s + 1], TQ):
+                t0.append(a)
+                n.append(min(TQ, qs[s + 1] - a))
+        with once_per_step():
+            plan = batch.attention_plan[key] = (new_ints(t0, device), new_ints(n, device), len(t0))
+    return plan
+
+
+def _page_stride(cache):
+    n = 1
+    for d in cache.shape[1:]:
+        n *= d
+    return n
+
+
+def headmix_prepare(proj, positions, slot_mapping, inv_freq, cache, H, G, D, E, page_size, act_dtype, has_gate=True,
+                    v_first=None, lam=None, v_keep=None):
+    """proj fp32 [T, >= (H+G)*D + G*E (+ H)]: rotates q and k heads on their first 2*len(inv_freq) channels (neighbouring
+    pairs), blends v with ``v_first`` by ``lam`` (a one-element tensor), writes k and v at ``slot_mapping`` into ``cache``
+    (None: no write) and returns (q [T, H*D] in ``act_dtype``, sigmoid gates fp32 [T, H] or None).  ``v_keep`` fp32
+    [T, G*E] receives the values as projected."""
+    lib = library("mixers")
+    T, ld = proj.shape
+    q = new_tensor((T, H * D), act_dtype, proj.device)
+    gate = new_tensor((T, H), torch.float32, proj.device) if has_gate else None
+    if cache is not None and cache.dtype != act_dtype:
+        raise KernelError("headmix_prepare: cache and activation dtypes differ")
+    if cache is None:
+        slot_mapping = None
+    stride = _page_stride(cache) if cache is not None else G * page_size * (D + E)
+    _check(lib, lib.forge_headmix_prepare(
+        _need(proj, "proj", torch.float32, 2), ld, _need(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _need(inv_freq, "inv_freq", torch.float32), _opt(v_first, "v_first", torch.float32), _opt(lam, "lam", torch.float32),
+        _opt(v_keep, "v_keep", torch.float32), _need(q, "q", act_dtype), _opt(cache, "cache"), _opt(gate, "gate", torch.float32),
+        dtype_code(act_dtype), T, H, G, D, E, 2 * inv_freq.numel(), page_size, stride, 1 if has_gate else 0, _stream()), "headmix_prepare")
+    return q, gate
+
+
+def headmix_attention(q, cache, group_batch, batch, H, G, D, E, page_size, scale, window=0, keep_first=0, mix=None, gate=None):
+    """Attention of every token of the step over its request's pages: ordinary softmax per head over the keys j <= i with
+    (i - j < window or j < keep_first) (window 0: all), the heads' weights mixed by ``mix`` fp32 [H, H] (None: not mixed),
+    applied to the values of each head's kv head, times ``gate`` fp32 [T, H] (None: no gate).  Returns [T, H*E] in q's type."""
+    lib = library("mixers")
+    T = q.shape[0]
+    single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
+    TQ, KT = headmix_tile_shape(H, G, D, E, single_tokens=single)
+    t0, tn, tiles = headmix_plan(batch, TQ, q.device)
+    out = new_tensor((T, H * E), q.dtype, q.device)
+    if cache.dtype != q.dtype:
+        raise KernelError("headmix_attention: q and cache dtypes differ")
+    _check(lib, lib.forge_headmix_attention(
+        _need(q, "q", ndim=2), _need(cache, "cache"), _need(group_batch.block_table, "block_table", torch.int32, 2),
+        _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+        _opt(tn, "tile_n", torch.int32), _opt(mix, "mix", torch.float32), _opt(gate, "gate", torch.float32), _need(out, "out", q.dtype),
+        dtype_code(q.dtype), tiles, H, G, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1], int(window or 0),
+        int(keep_first or 0), float(scale), TQ, KT, _stream()), "headmix_attention")
+    return out
+
+
+def _cols(t, off=0):
+    """(pointer, leading dimension) of the columns of fp32 matrix ``t`` from ``off`` on."""
+    if t is None:
+        return None, 0
+    return _need(t, "matrix", torch.float32, 2) + 4 * int(off), t.shape[1]
+
+
+STATE_SCANS = {"decay_bonus": 0, "delta": 1}
+
+
+def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=None, last_in=None, prev_off=0):
+    """The recurrence of a mixer with a [K, K] state per head (``kind``: "decay_bonus" or "delta", see csrc/recurrent.cu)
+    over the step's tokens, request by request, from and into ``state`` fp32 [slots, row].  r, k, v, x, y: (fp32 matrix,
+    first column) pairs with N*K columns from there; returns fp32 [T, N*K].  ``last_in`` ("decay_bonus"): the mixer's input
+    [T, W], whose last row per request is kept in the state row at ``prev_off``."""
+    lib = library("mixers")
+    T = r[0].shape[0]
+    out = new_tensor((T, N * K), torch.float32, r[0].device)
+    (rp, rl), (kp, kl), (vp, vl), (xp, xl) = _cols(*r), _cols(*k), _cols(*v), _cols(*x)
+    yp, yl = _cols(*y) if y is not None else (None, 0)
+    W = last_in.shape[1] if last_in is not None else 0
+    _check(lib, lib.forge_state_scan(
+        STATE_SCANS[kind], rp, rl, kp, kl, vp, vl, xp, xl, yp, yl, _need(w0, "w0", torch.float32), _opt(a0, "a0", torch.float32),
+        _opt(bonus, "bonus", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
+        _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(out, "out", torch.float32),
+        _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), batch.num_requests, N, K,
+        _stream()), "state_scan")
+    return out
+
+
+def token_shift(h, state, prev_off, batch, mu):
+    """[n, T, W] in h's type: h + (previous token's h - h) * mu[m]; the previous token of a request's first token of the
+    step is the row kept in its state (fp32 [slots, row], at ``prev_off``)."""
+    lib = library("mixers")
+    T, W = h.shape
+    n = mu.shape[0]
+    out = new_tensor((n, T, W), h.dtype, h.device)
+    _check(lib, lib.forge_token_shift(_need(h, "h", ndim=2), _need(state, "state", torch.float32, 2), state.shape[1], int(prev_off),
+                                      _need(batch.tok_req, "tok_req", torch.int32), _need(batch.q_start, "q_start", torch.int32),
+                                      _need(batch.slots, "slots", torch.int32), _need(mu, "mu", torch.float32, 2), _need(out, "out", h.dtype),
+                                      dtype_code(h.dtype), T, W, n, _stream()), "token_shift")
+    return out
+
+
+HEAD_GATES = {"sigmoid": 0, "silu": 1}
+
+
+def head_finish(o, weight, gate, N, K, eps, gate_activation, out_dtype):
+    """o fp32 [T, N*K]: every head divided by its root mean square (eps inside the root), times ``weight`` fp32 [N*K], times
+    the activation of ``gate`` ((fp32 matrix, first column)); [T, N*K] in ``out_dtype``."""
+    lib = library("mixers")
+    T = o.shape[0]
+    out = new_tensor((T, N * K), out_dtype, o.device)
+    gp, gl = _cols(*gate)
+    _check(lib, lib.forge_head_finish(_need(o, "o", torch.float32, 2), _need(weight, "weight", torch.float32), gp, gl,
+                                      _need(out, "out", out_dtype), dtype_code(out_dtype), T, N, K, float(eps),
+                                      HEAD_GATES[gate_activation], _stream()), "head_finish")
+    return out
+
+
+def tanh_rows(x, out_dtype, n=None):
+    """tanh of the first ``n`` columns of (fp32 matrix, first column) ``x``, [T, n] in ``out_dtype``."""
+    lib = library("mixers")
+    t, off = x
+    n = t.shape[1] - off if n is None else n
+    out = new_tensor((t.shape[0], n), out_dtype, t.device)
+    xp, xl = _cols(t, off)
+    _check(lib, lib.forge_tanh_rows(xp, xl, _need(out, "out", out_dtype), dtype_code(out_dtype), t.shape[0], n, _stream()), "tanh_rows")
     return out
 
 
@@ -1012,13 +1186,13 @@ def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_d
                                 n_kv_heads, head_dim, page_size, window=window or 0, scale=scale)
 
 
-EPILOGUES = {"none": 0, "accumulate": 1, "cast": 2, "swiglu": 3}
+EPILOGUES = {"none": 0, "accumulate": 1, "cast": 2, "swiglu": 3, "geglu": 5}
 
 
 def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None):
     """bf16 x [M,K] . w [N,K]^T on the tcgen05 tensor cores, fp32 accumulation.
     epilogue "none": fp32 [M,N] (added into ``accumulate_into`` when given); "cast": bf16 [M,N];
-    "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]."""
+    "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]; "geglu": the same with the tanh form of gelu."""
     lib = library("gemm_sm100")
     (M, K), (N, K2) = x.shape, w.shape
     if K != K2:
@@ -1033,9 +1207,9 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
     elif epilogue == "cast":
         out = new_tensor((M, N), torch.bfloat16, x.device) if out is None else out
         code, want_shape, want_dtype = EPILOGUES["cast"], (M, N), torch.bfloat16
-    elif epilogue == "swiglu":
+    elif epilogue in ("swiglu", "geglu"):
         out = new_tensor((M, N // 2), torch.bfloat16, x.device) if out is None else out
-        code, want_shape, want_dtype = EPILOGUES["swiglu"], (M, N // 2), torch.bfloat16
+        code, want_shape, want_dtype = EPILOGUES[epilogue], (M, N // 2), torch.bfloat16
     else:
         raise KernelError(f"gemm_sm100: unknown epilogue {epilogue!r}")
     if tuple(out.shape) != want_shape:

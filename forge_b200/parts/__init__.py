@@ -1,6 +1,7 @@
 from .base import (CATEGORIES, KVCacheSpec, Part, Runtime, StateSpec, build_part, register_part, registered_parts,
                    unregister_part)
-from . import attention, block, embedding, feedforward, norm, position  # noqa: F401  (register the built-in parts)
+from . import (attention, block, embedding, feedforward, headmix_attention, norm, position,  # noqa: F401  (register the
+               recurrent)                                                                    # built-in parts)
 from .block import build_block
 from .linear import Linear
 

@@ -41,10 +41,19 @@ class Runtime:
 @dataclass(frozen=True)
 class KVCacheSpec:
     """A mixer that keeps keys and values: pages of [2, num_kv_heads, page_size, head_dim].
-    ``window``: only the last ``window`` positions are ever read (None: all of them)."""
+    ``window``: only the last ``window`` positions are ever read (None: all of them), and, with ``keep_first``, the first
+    ``keep_first`` positions of the sequence, which are never given back.  ``v_head_dim``: size of a value head when
+    it is not the key's; a page is then one row, [num_kv_heads, page_size, head_dim] keys followed by [num_kv_heads,
+    page_size, v_head_dim] values."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
+
+    @property
+    def value_dim(self):
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 """Arrangements of a layer's parts around the fp32 residual stream.
 
 "pre_norm":  r += mixer(norm_in(r));  r += feed_forward(norm_post(r))
-(reference: src/inference/engines/generic_engine.cpp:931-938, 1045-1052, 1080).  The additions happen in
+(reference: src/inference/engines/generic_engine.cpp:931-938, 1045-1052, 1080).
+"parallel":  r += mixer(norm_a(r)) + feed_forward(norm_b(r)), both branches of the same r.  The additions happen in
 the epilogue of each part's last matrix product, in fp32.
 """
 from ..weights.loader import TensorSpec  # noqa: F401  (re-exported for part authors)
@@ -79,6 +80,43 @@ class PreNormBlock(Part):
         self.feed_forward.forward(x, residual)
 
 
+class ParallelBlock(Part):
+    """Both branches read the residual stream as the layer found it: the two norms run before either branch adds its
+    output.  ``norms``: {"mixer": spec, "feed_forward": spec or None}; a norm's spec carries its tensor's name."""
+    graph_safe = True
+
+    def sub_parts(self):
+        return [p for p in (self.mixer, self.feed_forward, self.norm_mixer, self.norm_ff) if p is not None]
+
+    def __init__(self, rt, layer_spec):
+        self.rt = rt
+        self.mixer = build_part("mixer", layer_spec.mixer, rt)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], rt)
+        ff_norm = layer_spec.norms.get("feed_forward")
+        self.norm_ff = None if ff_norm is None else build_part("norm", ff_norm, rt)
+
+    def _children(self):
+        return [p for p in (self.mixer, self.feed_forward, self.norm_mixer, self.norm_ff) if p is not None]
+
+    def tensor_specs(self):
+        specs = {}
+        for part in self._children():
+            specs.update(part.tensor_specs())
+        return specs
+
+    def bind(self, tensors):
+        for part in self._children():
+            part.bind({name: tensors[name] for name in part.tensor_specs() if name in tensors})
+
+    def forward(self, residual, batch, cache):
+        x = self.norm_mixer.forward(residual)
+        x_ff = None if self.norm_ff is None else self.norm_ff.forward(residual)
+        self.mixer.forward(x, batch, cache, residual)
+        if x_ff is not None:
+            self.feed_forward.forward(x_ff, residual)
+
+
 def build_block(layer_spec, rt):
     from .base import _REGISTRY
     from ..config.base import ConfigError
@@ -90,3 +128,4 @@ def build_block(layer_spec, rt):
 
 
 register_part("block", "pre_norm", PreNormBlock, replace=True)
+register_part("block", "parallel", ParallelBlock, replace=True)

@@ -1,6 +1,6 @@
 """Token embedding and output head.
 
-embedding: residual[t,:] = E[id_t,:] (fp32 residual stream).  lm_head: logits = x . W^T in fp32, with
+embedding: residual[t,:] = E[id_t,:] * scale (fp32 residual stream; scale 1 unless the design gives one).  lm_head: logits = x . W^T in fp32, with
 W = E when the embeddings are tied and the file has no head of its own
 (reference: src/inference/engines/transformer_engine.cpp:495-522, src/model/model_weights.cpp:28-33).
 """
@@ -12,8 +12,8 @@ from .linear import Linear
 
 class TokenEmbedding(Part):
     graph_safe = True
-    def __init__(self, rt, vocab_size, hidden_size, names=None):
-        self.rt, self.vocab_size, self.hidden_size = rt, vocab_size, hidden_size
+    def __init__(self, rt, vocab_size, hidden_size, names=None, scale=1.0):
+        self.rt, self.vocab_size, self.hidden_size, self.scale = rt, vocab_size, hidden_size, float(scale)
         self.names = {"weight": "weight", **(names or {})}
         self.table = None
 
@@ -28,7 +28,7 @@ class TokenEmbedding(Part):
         return self.table
 
     def forward(self, token_ids, status=None):
-        return kernels.embedding(token_ids, self.table, status=status)
+        return kernels.embedding(token_ids, self.table, status=status, scale=self.scale)
 
 
 class LMHead(Part):

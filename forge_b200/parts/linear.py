@@ -27,6 +27,7 @@ class Linear:
         """x [M,K] in rt.dtype.
         epilogue "none":   fp32 [M,N] (added into ``accumulate_into`` if given, which is then returned)
         epilogue "swiglu": rt.dtype [M,N/2], out[:,j] = silu(y[:,2j]) * y[:,2j+1]
+        epilogue "geglu":  the same with the tanh form of gelu as the gate's activation
         epilogue "cast":   rt.dtype [M,N]
         """
         if self.tensor_core:
@@ -35,8 +36,8 @@ class Linear:
             return kernels.gemm_simt(x, self.weight, bias=self.bias, out=accumulate_into,
                                      accumulate=accumulate_into is not None)
         y = kernels.gemm_simt(x, self.weight, bias=self.bias)
-        if epilogue == "swiglu":
-            return kernels.silu_mul_interleaved(y, self.rt.dtype)
+        if epilogue in ("swiglu", "geglu"):
+            return kernels.silu_mul_interleaved(y, self.rt.dtype, activation="silu" if epilogue == "swiglu" else "gelu_tanh")
         if epilogue == "cast":
             return y.to(self.rt.dtype)
         raise ValueError(f"unknown epilogue {epilogue!r}")

@@ -68,5 +68,25 @@ class NoPosition(RotaryEmbedding):
         super().__init__(rt, head_dim, 1.0)
 
 
+class PairedRotary(Part):
+    """Rotary encoding of neighbouring channels (2i, 2i+1) on the first ``rotary_dims`` channels of a head; the rest pass
+    unchanged.  Pair i turns by position * theta^(-2i/rotary_dims); the frequencies are worked out in 64-bit on the host
+    and kept as a small fp32 table, the angles and their sines are 32-bit on the device.  It offers no ``encode_and_store``:
+    the mixers that use it rotate inside their own prepare step (``kernels.headmix_prepare``) and ask for ``inv_freq``."""
+    graph_safe = True
+
+    def __init__(self, rt, head_dim, rotary_dims=None, theta=10000.0):
+        import torch
+        self.rt, self.head_dim, self.theta = rt, int(head_dim), float(theta)
+        self.rotary_dims = self.head_dim if rotary_dims is None else int(rotary_dims)
+        if self.rotary_dims % 2 or not 0 <= self.rotary_dims <= self.head_dim:
+            from ..config.base import ConfigError
+            raise ConfigError(f"rotary encoding of {self.rotary_dims} channels does not fit heads of {self.head_dim}")
+        i = torch.arange(self.rotary_dims // 2, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(1, self.rotary_dims))
+        self.inv_freq = freq.to(torch.float32).to(rt.device)
+
+
 register_part("position", "rope", RotaryEmbedding, replace=True)
+register_part("position", "rope_pairs", PairedRotary, replace=True)
 register_part("position", "none", NoPosition, replace=True)

@@ -1,0 +1,126 @@
+"""Mixers that carry a matrix of state per head from token to token instead of a cache of keys and values.
+
+Both have N heads of K channels, keep S [K, K] per head and request in 32-bit (a row of the layer's state tensor per
+request slot, zero at admission), make their decay from a low-rank projection, x = W2 tanh(W1 .) + w0, divide every head's
+output by its root mean square, multiply by a weight per channel and by a gate, and project back to the model's width.
+
+"wkv" (decay and bonus, with a look at the previous token):
+    each of r, k, v, g, w reads h + (h_prev - h) * mu_s;  w_t = exp(-exp(x_t));  gate = silu(g)
+    o_t = (S + diag(u) k_t v_t^T)^T r_t;   S <- diag(w_t) S + k_t v_t^T          (the previous token's h is state too)
+"general_delta" (generalized delta rule):
+    w_t = exp(-exp(-1/2) sigmoid(x_t));  a_t = sigmoid(Wa h + b);  n_t = k_t / sqrt(|k_t|^2 + 1e-6);  gate = sigmoid(g)
+    S <- diag(w_t) S - (a_t * n_t)(n_t^T S) + k_t v_t^T;   o_t = S^T r_t
+
+The rank of the decay's projection is read from the file's tensors (``rank`` is only what random weights take).
+"""
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError
+from ..weights.loader import TensorSpec
+from .base import Part, StateSpec, register_part
+from .linear import Linear
+
+
+class _StateMixer(Part):
+    graph_safe = True       # request boundaries and state rows come from the batch's device tensors (q_start, slots)
+    MATRICES = ()
+
+    def __init__(self, rt, hidden_size, num_heads, head_dim, eps, rank=16, names=None, prefix="mix."):
+        if head_dim > 128:
+            raise ConfigError(f"state mixers take heads of up to 128 channels, not {head_dim}")
+        self.rt, self.hidden_size, self.num_heads, self.head_dim = rt, hidden_size, num_heads, head_dim
+        self.eps, self.rank, self.prefix = float(eps), int(rank), prefix
+        self.names = dict(names or {})
+
+    def _n(self, short):
+        return self.names.get(short, self.prefix + short)
+
+    def _common_specs(self):
+        W, NK = self.hidden_size, self.num_heads * self.head_dim
+        specs = {self._n(m): TensorSpec((NK, W)) for m in self.MATRICES}
+        specs.update({self._n("w1"): TensorSpec((-1, W), default_shape=(self.rank, W)),
+                      self._n("w2"): TensorSpec((NK, -1), default_shape=(NK, self.rank)),
+                      self._n("w0"): TensorSpec((NK,), role="bias"), self._n("norm"): TensorSpec((NK,), role="norm"),
+                      self._n("o"): TensorSpec((W, NK))})
+        return specs
+
+    def _bind_common(self, tensors):
+        w1, w2 = tensors[self._n("w1")], tensors[self._n("w2")]
+        if w1.shape[0] != w2.shape[1]:
+            from ..weights.loader import WeightError
+            raise WeightError(self._n("w1"), wrong=[f"{self._n('w1')} has {w1.shape[0]} rows, {self._n('w2')} {w2.shape[1]} columns"])
+        self.w2 = Linear(self._matrix(w2), None, self.rt)
+        self.w0 = self._vector_f32(tensors[self._n("w0")])
+        self.norm = self._vector_f32(tensors[self._n("norm")])
+        self.o = Linear(self._matrix(tensors[self._n("o")]), None, self.rt)
+        return w1
+
+    def _decay_input(self, hidden):
+        """hidden: (fp32 matrix, first column) of W1's product; returns fp32 [T, N*K], W2 tanh(.) (w0 is added where
+        the decay is made)."""
+        return self.w2.forward(kernels.tanh_rows(hidden, self.rt.dtype, n=self.w2.in_features))
+
+
+class WKVMixer(_StateMixer):
+    MATRICES = ("r", "k", "v", "g")
+    SHIFTED = ("r", "k", "v", "g", "w")
+
+    def tensor_specs(self):
+        specs = self._common_specs()
+        specs.update({self._n("mu." + s): TensorSpec((self.hidden_size,), role="fraction") for s in self.SHIFTED})
+        specs[self._n("u")] = TensorSpec((self.num_heads, self.head_dim), role="bias")
+        return specs
+
+    def bind(self, tensors):
+        self.w1 = Linear(self._matrix(self._bind_common(tensors)), None, self.rt)
+        self.lin = {m: Linear(self._matrix(tensors[self._n(m)]), None, self.rt) for m in self.MATRICES}
+        self.mu = torch.stack([self._vector_f32(tensors[self._n("mu." + s)]) for s in self.SHIFTED]).contiguous()
+        self.bonus = self._vector_f32(tensors[self._n("u")]).reshape(-1).contiguous()
+
+    def cache_spec(self):
+        n = self.num_heads * self.head_dim * self.head_dim
+        return StateSpec((n + self.hidden_size,), torch.float32)      # the heads' matrices, then the previous token's input
+
+    def forward(self, x, batch, cache, residual):
+        N, K = self.num_heads, self.head_dim
+        prev_off = N * K * K
+        shifted = kernels.token_shift(x, cache.state, prev_off, batch, self.mu)            # [5, T, W]
+        r, k, v, g = (self.lin[m].forward(shifted[i]) for i, m in enumerate(self.MATRICES))
+        decay_in = self._decay_input((self.w1.forward(shifted[4]), 0))
+        o = kernels.state_scan("decay_bonus", (r, 0), (k, 0), (v, 0), (decay_in, 0), self.w0, cache.state, batch, N, K,
+                               bonus=self.bonus, last_in=x, prev_off=prev_off)
+        y = kernels.head_finish(o, self.norm, (g, 0), N, K, self.eps, "silu", self.rt.dtype)
+        self.o.forward(y, accumulate_into=residual)
+
+
+class GeneralDeltaMixer(_StateMixer):
+    MATRICES = ("r", "k", "v", "g", "a")
+
+    def tensor_specs(self):
+        specs = self._common_specs()
+        specs[self._n("a.b")] = TensorSpec((self.num_heads * self.head_dim,), role="bias")
+        return specs
+
+    def bind(self, tensors):
+        w1 = self._bind_common(tensors)
+        # r, k, v, g, a and the decay's first matrix read the same input: one product
+        self.proj = Linear(self._matrix(torch.cat([tensors[self._n(m)] for m in self.MATRICES] + [w1], dim=0)), None, self.rt)
+        self.a0 = self._vector_f32(tensors[self._n("a.b")])
+
+    def cache_spec(self):
+        return StateSpec((self.num_heads * self.head_dim * self.head_dim,), torch.float32)
+
+    def forward(self, x, batch, cache, residual):
+        N, K = self.num_heads, self.head_dim
+        NK = N * K
+        p = self.proj.forward(x)                                     # fp32 [T, 5*N*K + rank]: r | k | v | g | a | hidden
+        decay_in = self._decay_input((p, 5 * NK))
+        o = kernels.state_scan("delta", (p, 0), (p, NK), (p, 2 * NK), (decay_in, 0), self.w0, cache.state, batch, N, K,
+                               y=(p, 4 * NK), a0=self.a0)
+        y = kernels.head_finish(o, self.norm, (p, 3 * NK), N, K, self.eps, "sigmoid", self.rt.dtype)
+        self.o.forward(y, accumulate_into=residual)
+
+
+register_part("mixer", "wkv", WKVMixer, replace=True)
+register_part("mixer", "general_delta", GeneralDeltaMixer, replace=True)

@@ -8,7 +8,7 @@ The table of names is the Hugging Face column of the reference's mapping (tools/
 src/model/weight_mapper.cpp:11-29); each part owns the names of its own tensors.
 """
 from dataclasses import dataclass
-from typing import Dict, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -37,7 +37,16 @@ class TensorSpec:
     shape: Tuple[int, ...]
     required: bool = True
     integer: bool = False        # an integer table (kept int32) rather than floating-point weights
-    role: str = "matrix"         # "matrix" | "embedding" | "norm" | "bias": how random weights are drawn for it
+    # how random weights are drawn for it: "matrix" | "embedding" | "norm" | "bias" | "fraction" (uniform in 0..1) |
+    # "head_mix" (the unit matrix plus noise)
+    role: str = "matrix"
+    # a size of -1 in ``shape`` is given by the file alone (the part reads it when it binds); ``default_shape`` is what
+    # random weights take for such a tensor
+    default_shape: Optional[Tuple[int, ...]] = None
+
+
+def shape_fits(file_shape, spec_shape):
+    return len(file_shape) == len(spec_shape) and all(w == -1 or int(f) == w for f, w in zip(file_shape, spec_shape))
 
 
 def check_tensors(where, expected: Dict[str, TensorSpec], present: Dict[str, Tuple[Tuple[int, ...], torch.dtype]]):
@@ -48,7 +57,7 @@ def check_tensors(where, expected: Dict[str, TensorSpec], present: Dict[str, Tup
         if n not in present:
             continue
         shape, dt = present[n]
-        if tuple(shape) != tuple(s.shape):
+        if not shape_fits(tuple(shape), tuple(s.shape)):
             wrong.append(f"{n}: file has {list(shape)}, model needs {list(s.shape)}")
         elif s.integer and dt not in (torch.int32, torch.int64):
             wrong.append(f"{n}: file has {dt}, model needs an integer table")
@@ -82,4 +91,4 @@ def load_tensors(model_dir, expected: Dict[str, TensorSpec]):
             f.close()
 
 
-__all__ = ["WeightError", "TensorSpec", "SafetensorsError", "check_tensors", "load_tensors"]
+__all__ = ["WeightError", "TensorSpec", "shape_fits", "SafetensorsError", "check_tensors", "load_tensors"]

@@ -23,8 +23,19 @@ def random_tensors(config, seed=0, std=0.02, embed_std=None, norm_std=0.0, bias_
     for name, spec in model.tensor_specs().items():
         if not spec.required:
             continue
+        shape = tuple(spec.shape)
+        if -1 in shape:
+            if spec.default_shape is None:
+                raise ValueError(f"{name}: a size is left to the file and no default is given for random weights")
+            shape = tuple(spec.default_shape)
+        spec = type(spec)(shape, spec.required, spec.integer, spec.role)
         if spec.integer:
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        elif spec.role == "fraction":
+            out[name] = torch.rand(spec.shape, generator=gen, dtype=torch.float32, device=device).to(dtype)
+        elif spec.role == "head_mix":
+            t = torch.eye(spec.shape[0], dtype=torch.float32, device=device)
+            out[name] = (t + torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * 0.3).to(dtype)
         elif spec.role == "norm":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
             if norm_std:
