@@ -97,7 +97,7 @@ def write_safetensors(path, tensors, metadata=None):
         t = t.detach().contiguous().cpu()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} of {name}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)
