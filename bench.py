@@ -162,7 +162,15 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-shapes", action="store_true", help="skip the Llama-3-8B and Qwen2.5-7B shaped points")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
+    ap.add_argument("--design", default=None, choices=["zatupel"],
+                    help="instead of the default workload: prefill and decode speed of that design at a few layer sizes, "
+                         "beside the LLaMA decoder of equal width, depth and head counts")
     a = ap.parse_args()
+    if a.design == "zatupel" and a.impl != "reference":
+        if a.gpus != 1:
+            print(json.dumps({"error": "forge_b200 is a single-GPU engine: bench.py runs at --gpus 1 only", "n_gpus": a.gpus}))
+            return 2
+        return design_arm(a)
     if a.impl == "reference":
         return reference_arm(a)
     if a.gpus != 1:
@@ -388,10 +396,122 @@ class ShapeBench:
         for _ in range(3):
             run()
         ms = self.timed(run, reps) / reps
+        return ms, self.prefill_flops(T)
+
+    def prefill_flops(self, T):
+        cfg = self.cfg
         per_layer, head = matmul_params(cfg)
         L = cfg.num_hidden_layers
-        flops = 2 * T * L * per_layer + L * 2 * T * T * cfg.head_dim * cfg.num_attention_heads + 2 * head
-        return ms, flops
+        return 2 * T * L * per_layer + L * 2 * T * T * cfg.head_dim * cfg.num_attention_heads + 2 * head
+
+
+def zatupel_shape(width, layers, heads, kv_heads, dim, ff, state_heads, state_dim, rank, window, vocab):
+    """A Zatupel configuration at a real model's layer sizes: attention, wkv, attention, general_delta in turn, value
+    heads as large as key heads, four kept first tokens, every attention layer but none blends values with the first."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "v_mix": True,
+                                          "mask": {"size": window, "keep_first": 4}, "rot": {"dims": dim, "base": 10000.0},
+                                          "scale": dim ** -0.5}, "mlp": {"kind": "dense", "ff": ff}}
+    state = lambda kind: {"type": kind, "mixer": {"heads": state_heads, "dim": state_dim, "rank": rank},
+                          "mlp": {"kind": "dense", "ff": ff}}
+    order = [att, state("wkv"), att, state("general_delta")]
+    return {"architecture": "Zatupel", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "max_positions": 8192, "layers": [order[i % 4] for i in range(layers)]}
+
+
+def zatupel_matmul_params(cfg):
+    """Matrix elements of all layers, and of the head."""
+    W, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            total += W * (H * D + G * D + G * E + H) + W * H * E
+        else:
+            NK, R = m["heads"] * m["dim"], m["rank"]
+            total += W * NK * (5 if layer["type"] == "wkv" else 6) + R * (W + NK)
+        if layer.get("mlp"):
+            total += 3 * W * layer["mlp"]["ff"]
+    return total, cfg.vocab * W
+
+
+class ZatupelBench(ShapeBench):
+    """ShapeBench's measurements for a configuration of the other architecture: only bytes and FLOPs are counted otherwise."""
+
+    def decode_bytes(self, B, ctx):
+        """Every matrix once, and per request the keys and values inside the window (and the kept first) and the state
+        matrices, read and written."""
+        cfg = self.cfg
+        layers, head = zatupel_matmul_params(cfg)
+        total = 2 * (layers + head)
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "attention":
+                seen = min(ctx, m["mask"]["size"] + m["mask"].get("keep_first", 0))
+                total += B * seen * m["kv_heads"] * (m["dim"] + m["vdim"]) * 2
+            else:
+                total += B * 2 * 4 * m["heads"] * m["dim"] * m["dim"]
+        return total
+
+    def prefill_flops(self, T):
+        cfg = self.cfg
+        layers, head = zatupel_matmul_params(cfg)
+        flops = 2 * T * layers + 2 * head
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "attention":
+                seen = sum(min(i + 1, m["mask"]["size"] + m["mask"].get("keep_first", 0)) for i in range(T))
+                flops += 2 * seen * m["heads"] * (m["dim"] + m["vdim"])
+            else:
+                flops += T * m["heads"] * m["dim"] * m["dim"] * (6 if layer["type"] == "wkv" else 8)
+        return flops
+
+
+def design_arm(a):
+    """Prefill and decode speed of the Zatupel design at a few layer sizes (random weights), each beside the LLaMA decoder
+    of the same width, depth, head counts and feed-forward width run the same way: decode device-timed at batch 1, 8 and
+    64 after 512-token prompts, one prompt step of 2,048 tokens.  One JSON line."""
+    import torch
+    torch.cuda.set_device(0)
+    pk = peaks()
+    a.warmup = max(a.warmup, 3)
+    steps = min(a.steps, 64)
+    sizes = {
+        # TinyLlama-1.1B's layer sizes, 8 layers
+        "w2048": dict(width=2048, layers=8, heads=32, kv_heads=4, dim=64, ff=5632, state_heads=32, state_dim=64, rank=64,
+                      window=1024, vocab=32000),
+        # Llama-3-8B's layer sizes, 4 layers
+        "w4096": dict(width=4096, layers=4, heads=32, kv_heads=8, dim=128, ff=14336, state_heads=64, state_dim=64, rank=64,
+                      window=1024, vocab=32000),
+    }
+    out = {"design": "zatupel", "impl": "forge_b200", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": a.warmup,
+           "data": "synthetic: random-init bf16 weights, uniform-random token ids", "peaks": pk["source"], "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, z in sizes.items():
+        llama = dict(architectures=["LlamaForCausalLM"], vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["ff"],
+                     num_hidden_layers=z["layers"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                     head_dim=z["dim"], rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=8192)
+        row = {}
+        for arch, shape, maker in (("zatupel", zatupel_shape(**z), ZatupelBench), ("llama", llama, ShapeBench)):
+            b = maker(shape, PROMPT_LEN, 64, steps, a.warmup, a.block_size, prefill_tokens=PREFILL_TOKENS)
+            r = {}
+            for B in (1, 8, 64):
+                v, ms, launches, ctx = b.decode_device(B)
+                r[f"decode_b{B}_tok_s"] = round(v, 1)
+                r[f"decode_b{B}_ms"] = round(ms, 4)
+                r[f"decode_b{B}_hbm_frac"] = round(b.decode_bytes(B, ctx) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                r[f"decode_b{B}_launches_per_step"] = launches // steps
+            ms, flops = b.prefill(reps=3)
+            r["prefill_tok_s"] = round(PREFILL_TOKENS / ms * 1e3, 1)
+            r["prefill_ms"] = round(ms, 3)
+            r["prefill_tensor_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+            row[arch] = r
+            b.close()
+            del b
+        out["sizes"][name] = dict(row, shape=z)
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
 
 
 def qwen_mixed_serving(a, pk):

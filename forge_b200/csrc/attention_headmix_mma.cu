@@ -1,0 +1,291 @@
+// Tensor-core form (bf16 operands, fp32 sums) of the attention whose heads exchange their weights after the softmax,
+// for prompt portions and single tokens alike; see attention_headmix.cu for the definition and the cache layout.
+//
+// The exchange  w_h = sum_g mix[h, g] p_g  is linear, so it can be taken after the values:
+//     o_h(i) = gate_h(i) * sum_g mix[h, g] * ( p_g(i, .) V_kv(h) )
+// The first kernel is therefore an ordinary one-pass attention per head g (running maximum and sum, nothing to meet
+// between heads) whose value matrix is ALL key/value heads' values side by side, G*E columns: it leaves, normalised,
+// u[i, g, :] = p_g(i, .) [V_0 | V_1 | ... ] in fp32.  The second kernel takes the sum over g for every head h from the
+// columns of h's own key/value head and applies the gate.  The price is G times the value product of an attention
+// without the exchange; what it buys is that no head waits for another and the weights never leave the registers.
+//
+// A CTA of four warps takes a tile of up to 64 rows = tokens x the query heads of ONE key/value head (consecutive
+// tokens of one request; a single token brings H/G rows), one chunk of VC value columns, and walks the keys in tiles
+// of 64 positions that start at multiples of 64: first the kept first positions below the window, then the window.
+// mma.sync m16n8k16 (the legacy tensor path): S = Q K^T with K rows as the column-major operand, O += P V with V
+// through ldmatrix.trans.
+#include "common.cuh"
+#include "checks.cuh"
+
+namespace {
+
+constexpr int BM = 64, BN = 64, kThreads = 128, kPad = 8;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ bool visible(int pos, int j, int window, int keep_first) {
+    return j <= pos && (window <= 0 || pos - j < window || j < keep_first);
+}
+
+// u fp32 [T, H, GE] (GE = G*E): u[t, g, :] = softmax_j(scale q_g(t) . k_kv(g)(j)) [v_0(j) | ... | v_{G-1}(j)].
+template <int VC>
+__global__ void __launch_bounds__(kThreads)
+headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
+                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
+                   const int32_t* __restrict__ tile_n, float* __restrict__ u, int H, int G, int D, int E, int page_size,
+                   long long page_stride, int max_pages, int window, int keep_first, float scale) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int tile = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * VC;
+    const int t0 = tile_t0 ? tile_t0[tile] : tile;
+    const int nq = tile_n ? tile_n[tile] : 1;
+    if (!FORGE_TOKEN_OK(t0) || !FORGE_TOKEN_OK(t0 + nq - 1)) return;
+    const int Gq = H / G, rows = nq * Gq, GE = G * E;
+    const int pos0 = positions[t0], pos_last = pos0 + nq - 1;
+    const int32_t* table = block_table + (size_t)tok_req[t0] * max_pages;
+    const int DP = D + kPad, VP = VC + kPad;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][D + 8]
+    __nv_bfloat16* Ks = Qs + BM * DP;                                     // [BN][D + 8]
+    __nv_bfloat16* Vs = Ks + BN * DP;                                     // [BN][VC + 8]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+    // queries: row r = token t0 + r / Gq, head c * Gq + r % Gq
+    const int dchunks = D >> 3;
+    for (int i = tid; i < BM * dchunks; i += kThreads) {
+        const int r = i / dchunks, ch = i % dchunks;
+        uint4 val = zero4;
+        if (r < rows)
+            val = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / Gq) * H + c * Gq + r % Gq) * D + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * DP + ch * 8) = val;
+    }
+
+    float oacc[VC / 8][4];
+#pragma unroll
+    for (int i = 0; i < VC / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+    float row_m[2] = {-INFINITY, -INFINITY}, row_l[2] = {0.f, 0.f};
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;           // this thread's two rows
+    const int pos_lo = pos0 + min(r_lo, rows - 1) / Gq, pos_hi = pos0 + min(r_hi, rows - 1) / Gq;
+    const bool live_lo = r_lo < rows, live_hi = r_hi < rows;
+
+    const int win_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int kept_hi = window > 0 ? min(keep_first, win_lo) : 0;
+    const int kept_tiles = (kept_hi + BN - 1) / BN;
+    const int first_win_tile = max(kept_tiles, win_lo / BN), last_tile = pos_last / BN;
+    const int n_tiles = kept_tiles + (last_tile - first_win_tile + 1);
+    const float sl2 = scale * 1.4426950408889634f;                        // scores in units of log2(e)
+    const int vchunks = VC >> 3;
+
+    for (int ti = 0; ti < n_tiles; ++ti) {
+        const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
+        const int j0 = kt * BN;
+        __syncthreads();                                                  // the tile before is done with Ks and Vs
+        for (int i = tid; i < BN * dchunks; i += kThreads) {
+            const int jj = i / dchunks, ch = i % dchunks, j = j0 + jj;
+            uint4 val = zero4;
+            if (j <= pos_last) {
+                const int page = table[j / page_size];
+                if (page >= 0 && FORGE_PAGE_OK(page))
+                    val = *reinterpret_cast<const uint4*>(cache + (size_t)page * page_stride + ((size_t)c * page_size + j % page_size) * D + ch * 8);
+            }
+            *reinterpret_cast<uint4*>(Ks + jj * DP + ch * 8) = val;
+        }
+        for (int i = tid; i < BN * vchunks; i += kThreads) {
+            const int jj = i / vchunks, ch = i % vchunks, j = j0 + jj, col = v0 + ch * 8;
+            uint4 val = zero4;
+            if (j <= pos_last && col < GE) {
+                const int page = table[j / page_size];
+                if (page >= 0 && FORGE_PAGE_OK(page))
+                    val = *reinterpret_cast<const uint4*>(cache + (size_t)page * page_stride + (size_t)G * page_size * D +
+                                                          ((size_t)(col / E) * page_size + j % page_size) * E + col % E);
+            }
+            *reinterpret_cast<uint4*>(Vs + jj * VP + ch * 8) = val;
+        }
+        __syncthreads();
+
+        // S = Q K^T for this warp's 16 rows and the tile's 64 keys
+        float sacc[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+        for (int k0 = 0; k0 < D; k0 += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * DP + k0 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; nt += 2) {
+                uint32_t b[4];      // keys nt*8 .. nt*8+15: (b0, b1) of the first eight, (b0, b1) of the next eight
+                ldmatrix_x4(b, Ks + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * DP + k0 + ((lane >> 3) & 1) * 8);
+                mma_bf16(sacc[nt], a, b[0], b[1]);
+                mma_bf16(sacc[nt + 1], a, b[2], b[3]);
+            }
+        }
+        // scale, mask, and the tile's maximum per row
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const bool hi = e >= 2;
+                const bool ok = (hi ? live_hi : live_lo) && visible(hi ? pos_hi : pos_lo, j, window, keep_first);
+                const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
+                sacc[nt][e] = s;
+                tmax[hi] = fmaxf(tmax[hi], s);
+            }
+        }
+        float alpha[2], base[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+            const float m_new = fmaxf(row_m[h], tmax[h]);
+            base[h] = m_new == -INFINITY ? 0.f : m_new;                   // a row that has seen nothing yet
+            alpha[h] = exp2f(row_m[h] - base[h]);                         // exp2(-inf) = 0
+            row_m[h] = m_new;
+        }
+        float tsum[2] = {0.f, 0.f};
+        uint32_t pa[BN / 16][4];                                          // P as the A operand, 16 keys per k-step
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+            const float p0 = exp2f(sacc[nt][0] - base[0]), p1 = exp2f(sacc[nt][1] - base[0]);
+            const float p2 = exp2f(sacc[nt][2] - base[1]), p3 = exp2f(sacc[nt][3] - base[1]);
+            tsum[0] += p0 + p1;
+            tsum[1] += p2 + p3;
+            pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 1);
+            tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 2);
+            row_l[h] = row_l[h] * alpha[h] + tsum[h];
+        }
+#pragma unroll
+        for (int i = 0; i < VC / 8; ++i) {
+            oacc[i][0] *= alpha[0];
+            oacc[i][1] *= alpha[0];
+            oacc[i][2] *= alpha[1];
+            oacc[i][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int nt = 0; nt < VC / 8; nt += 2) {
+                uint32_t b[4];      // keys kk*16 .. +15 (rows), columns nt*8 .. +15: matrices (k lo, n lo), (k hi, n lo), (k lo, n hi), (k hi, n hi)
+                ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nt * 8 + (lane >> 4) * 8);
+                mma_bf16(oacc[nt], pa[kk], b[0], b[1]);
+                mma_bf16(oacc[nt + 1], pa[kk], b[2], b[3]);
+            }
+        }
+    }
+    // normalise and store this chunk's columns of u
+    const float inv[2] = {row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f, row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = h ? r_hi : r_lo;
+        if (r >= rows) continue;
+        float* dst = u + ((size_t)(t0 + r / Gq) * H + c * Gq + r % Gq) * GE;
+#pragma unroll
+        for (int nt = 0; nt < VC / 8; ++nt) {
+            const int col = v0 + nt * 8 + (lane & 3) * 2;
+            if (col < GE) *reinterpret_cast<float2*>(dst + col) = make_float2(oacc[nt][2 * h] * inv[h], oacc[nt][2 * h + 1] * inv[h]);
+        }
+    }
+}
+
+// out[t, h, e] = gate[t, h] * sum_g mix[h, g] u[t, g, kv(h) * E + e]      (mix null: u[t, h, ...] alone)
+__global__ void __launch_bounds__(128)
+headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ mix, const float* __restrict__ gate,
+                       __nv_bfloat16* __restrict__ out, int H, int G, int E) {
+    extern __shared__ float mx[];
+    forge::pdl_launch_dependents();
+    if (mix) for (int i = threadIdx.x; i < H * H; i += blockDim.x) mx[i] = mix[i];
+    forge::pdl_wait();
+    __syncthreads();
+    const int t = blockIdx.x, GE = G * E, Gq = H / G;
+    const float* ut = u + (size_t)t * H * GE;
+    for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
+        const int h = i / E, e = i % E, col = (h / Gq) * E + e;
+        float a;
+        if (mix) {
+            a = 0.f;
+            for (int g = 0; g < H; ++g) a = fmaf(mx[h * H + g], ut[(size_t)g * GE + col], a);
+        } else {
+            a = ut[(size_t)h * GE + col];
+        }
+        if (gate) a *= gate[(size_t)t * H + h];
+        out[(size_t)t * H * E + i] = __float2bfloat16_rn(a);
+    }
+}
+
+forge::PerDeviceFlag g_attr_done[3];
+
+template <int VC>
+int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
+               const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u,
+               int H, int G, int D, int E, int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale) {
+    bool& done = g_attr_done[which].current();
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return forge::check_launch("headmix_attention_mma (shared memory)", e);
+        done = true;
+    }
+    return forge::check_launch("headmix_attention_mma",
+                               forge::launch(headmix_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions,
+                                             t0, tn, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take these sizes: key heads of a multiple of 16 channels up to 128, value heads of a
+// multiple of 8 channels, at most 64 query heads per key/value head, at most 96 heads (the exchange matrix in shared memory).
+extern "C" int forge_headmix_mma_supports(int H, int G, int D, int E) {
+    return (H > 0 && G > 0 && H % G == 0 && H / G <= BM && H <= 96 && D % 16 == 0 && D >= 16 && D <= 128 && E % 8 == 0 && E > 0) ? 1 : 0;
+}
+
+// q bf16 [T, H*D]; u fp32 [T, H, G*E] (scratch); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive tokens of one
+// request with tile_n * (H/G) <= 64 (both null: one token per tile, num_tiles = T).  mix fp32 [H, H] or null; gate fp32
+// [T, H] or null.
+extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
+                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* mix,
+                                           const float* gate, float* u, void* out, int T, int num_tiles, int H, int G, int D, int E,
+                                           int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale,
+                                           cudaStream_t stream) {
+    if (!forge_headmix_mma_supports(H, G, D, E)) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_attention_mma: H=%d G=%d D=%d E=%d", H, G, D, E);
+    if (T < 0 || num_tiles < 0 || page_size <= 0 || max_pages <= 0 || keep_first < 0 || (tile_t0 == nullptr) != (tile_n == nullptr))
+        return forge::fail(FORGE_ERR_ARG, "headmix_attention_mma: bad arguments");
+    if (T == 0 || num_tiles == 0) return FORGE_OK;
+    const int GE = G * E;
+    int VC = 64;                        // the chunk width that wastes the fewest columns; among equals the widest
+    for (int cand : {128, 256})
+        if ((GE + cand - 1) / cand * cand <= (GE + VC - 1) / VC * VC) VC = cand;
+    const int chunks = (GE + VC - 1) / VC;
+    const size_t smem = sizeof(__nv_bfloat16) * ((size_t)(BM + BN) * (D + kPad) + (size_t)BN * (VC + kPad));
+    const dim3 grid(num_tiles, G, chunks);
+    const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
+    const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
+    int rc;
+    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    if (rc != FORGE_OK) return rc;
+    return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T), dim3(128), mix ? sizeof(float) * H * H : 0, stream, 1,
+                                                                (const float*)u, mix, gate, (__nv_bfloat16*)out, H, G, E));
+}
+
+FORGE_DEFINE_CHECKS_ENTRY(attention_headmix_mma)

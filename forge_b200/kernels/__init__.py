@@ -61,6 +61,8 @@ _SIGNATURES = {
     "mixers": {
         "forge_headmix_prepare": [_P, _I] + [_P] * 9 + [_I] * 8 + [_LL, _I, _P],
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
+        "forge_headmix_mma_supports": [_I, _I, _I, _I],
+        "forge_headmix_attention_mma": [_P] * 11 + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -81,7 +83,7 @@ _libs = {}
 # tested before use, a bad one raises bit 4 of the step's status word and is skipped.  The entries that tell a
 # library the bounds, per library (one per source file that checks):
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
-                  "mixers": ["forge_checks_configure_attention_headmix"],
+                  "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -682,13 +684,15 @@ def headmix_smem_bytes(H, G, D, E, TQ, KT):
 
 
 def headmix_tile_shape(H, G, D, E, single_tokens=False):
-    """(tokens per tile, keys per chunk) of the attention kernel for these head counts and sizes: the largest that fit
-    the CTA's shared memory.  ``single_tokens``: a step of one token per request."""
-    for KT in (64, 32, 16, 8, 4, 2, 1):
-        for TQ in ((1,) if single_tokens else (16, 8, 4, 2, 1)):
-            if headmix_smem_bytes(H, G, D, E, TQ, KT) <= HEADMIX_SMEM_LIMIT:
-                return TQ, KT
-    raise KernelError(f"headmix attention: {H} heads of {D}/{E} channels do not fit a CTA's shared memory")
+    """(tokens per tile, keys per chunk) of the attention kernel for these head counts and sizes: of the shapes that fit
+    the CTA's shared memory the one with the most (token, key) pairs, among equals the one with more tokens (a chunk's keys
+    are loaded once per tile).  ``single_tokens``: a step of one token per request."""
+    fits = [(TQ * KT, TQ, KT) for KT in (64, 32, 16, 8, 4, 2, 1) for TQ in ((1,) if single_tokens else (16, 8, 4, 2, 1))
+            if headmix_smem_bytes(H, G, D, E, TQ, KT) <= HEADMIX_SMEM_LIMIT]
+    if not fits:
+        raise KernelError(f"headmix attention: {H} heads of {D}/{E} channels do not fit a CTA's shared memory")
+    _, TQ, KT = max(fits)
+    return TQ, KT
 
 
 def headmix_plan(batch, TQ, device):
@@ -745,6 +749,19 @@ def headmix_attention(q, cache, group_batch, batch, H, G, D, E, page_size, scale
     applied to the values of each head's kv head, times ``gate`` fp32 [T, H] (None: no gate).  Returns [T, H*E] in q's type."""
     lib = library("mixers")
     T = q.shape[0]
+    if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_headmix_mma_supports.fn(H, G, D, E):
+        # tensor cores: one pass per head over all key/value heads' values, then the exchange between heads
+        t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
+        u = new_tensor((T, H, G * E), torch.float32, q.device)
+        out = new_tensor((T, H * E), q.dtype, q.device)
+        _check(lib, lib.forge_headmix_attention_mma(
+            _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
+            _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+            _opt(tn, "tile_n", torch.int32), _opt(mix, "mix", torch.float32), _opt(gate, "gate", torch.float32), _need(u, "u", torch.float32),
+            _need(out, "out", torch.bfloat16), T, tiles, H, G, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
+            int(window or 0), int(keep_first or 0), float(scale), _stream()), "headmix_attention_mma")
+        count_launches(1)          # the kernel that takes the sum over heads
+        return out
     single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
     TQ, KT = headmix_tile_shape(H, G, D, E, single_tokens=single)
     t0, tn, tiles = headmix_plan(batch, TQ, q.device)

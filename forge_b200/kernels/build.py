@@ -30,7 +30,7 @@ LIBRARIES = {
     # bf16 tcgen05/TMEM paged attention for prompt portions, head sizes 64 and 128 (built per head size)
     "attention_sm100": ["attention_sm100.cu"],
     # attention whose heads exchange weights, over a window with kept first tokens; mixers with a matrix of state per head
-    "mixers": ["attention_headmix.cu", "recurrent.cu"],
+    "mixers": ["attention_headmix.cu", "attention_headmix_mma.cu", "recurrent.cu"],
     # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)
     "decode_layers": ["decode_layers.cu"],
 }

@@ -122,7 +122,8 @@ def _visible(i, j, size, keep):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("page_size", [8, 64])
-def test_one_key_that_stands_out(dtype, page_size):
+@pytest.mark.parametrize("D, E", [(8, 4), (16, 8)])          # the second pair is one that the tensor-core kernel takes in bfloat16
+def test_one_key_that_stands_out(dtype, page_size, D, E):
     """Keys are zero except one, far away among hundreds, at a window's edge or among the kept first, whose score is
     huge for head 0; values carry their position.  Head 0 (before the heads' exchange) returns that position if it is
     visible and the mean of the visible positions if it is not; head 1 always the mean.  For tokens of a prompt portion
@@ -131,7 +132,7 @@ def test_one_key_that_stands_out(dtype, page_size):
     from forge_b200.cache import CacheStorage
     from forge_b200.engine import StepEntry, build_step_batch
     from forge_b200.parts import KVCacheSpec
-    H, G, D, E, size, keep, N, M = 2, 1, 8, 4, 21, 3, 300, 27
+    H, G, size, keep, N, M = 2, 1, 21, 3, 300, 27
     dev = torch.device(DEV)
     mix = torch.tensor([[0.7, 0.3], [0.2, 0.8]], device=DEV)
     storage = CacheStorage([KVCacheSpec(G, D, size, v_head_dim=E, keep_first=keep)], [None], page_size, 64 * 8 // page_size, 2, dtype, dev)
