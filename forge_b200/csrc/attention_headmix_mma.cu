@@ -33,6 +33,15 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16 bytes from global to shared memory without a stop in registers; ok == false writes zeros instead
+__device__ __forceinline__ void copy16_async(void* dst, const void* src, bool ok) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -60,8 +69,9 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int32_t* table = block_table + (size_t)tok_req[t0] * max_pages;
     const int DP = D + kPad, VP = VC + kPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][D + 8]
-    __nv_bfloat16* Ks = Qs + BM * DP;                                     // [BN][D + 8]
-    __nv_bfloat16* Vs = Ks + BN * DP;                                     // [BN][VC + 8]
+    const int stage = BN * (DP + VP);                                     // elements of one buffer: a key tile and a value tile
+    __nv_bfloat16* Ks = Qs + BM * DP;                                     // 2 x [BN][D + 8]
+    __nv_bfloat16* Vs = Ks + BN * DP;                                     // 2 x [BN][VC + 8], each behind its key tile
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
@@ -91,32 +101,53 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const float sl2 = scale * 1.4426950408889634f;                        // scores in units of log2(e)
     const int vchunks = VC >> 3;
 
-    for (int ti = 0; ti < n_tiles; ++ti) {
+    // key and value tiles go through two buffers: tile ti + 1 is on its way while tile ti is worked on
+    auto fetch = [&](int ti, int buf) {
         const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
         const int j0 = kt * BN;
-        __syncthreads();                                                  // the tile before is done with Ks and Vs
+        __nv_bfloat16* Kb = Ks + buf * stage;
+        __nv_bfloat16* Vb = Vs + buf * stage;
         for (int i = tid; i < BN * dchunks; i += kThreads) {
             const int jj = i / dchunks, ch = i % dchunks, j = j0 + jj;
-            uint4 val = zero4;
+            const __nv_bfloat16* src = cache;
+            bool ok = false;
             if (j <= pos_last) {
                 const int page = table[j / page_size];
-                if (page >= 0 && FORGE_PAGE_OK(page))
-                    val = *reinterpret_cast<const uint4*>(cache + (size_t)page * page_stride + ((size_t)c * page_size + j % page_size) * D + ch * 8);
+                if (page >= 0 && FORGE_PAGE_OK(page)) {
+                    ok = true;
+                    src = cache + (size_t)page * page_stride + ((size_t)c * page_size + j % page_size) * D + ch * 8;
+                }
             }
-            *reinterpret_cast<uint4*>(Ks + jj * DP + ch * 8) = val;
+            copy16_async(Kb + jj * DP + ch * 8, src, ok);
         }
         for (int i = tid; i < BN * vchunks; i += kThreads) {
             const int jj = i / vchunks, ch = i % vchunks, j = j0 + jj, col = v0 + ch * 8;
-            uint4 val = zero4;
+            const __nv_bfloat16* src = cache;
+            bool ok = false;
             if (j <= pos_last && col < GE) {
                 const int page = table[j / page_size];
-                if (page >= 0 && FORGE_PAGE_OK(page))
-                    val = *reinterpret_cast<const uint4*>(cache + (size_t)page * page_stride + (size_t)G * page_size * D +
-                                                          ((size_t)(col / E) * page_size + j % page_size) * E + col % E);
+                if (page >= 0 && FORGE_PAGE_OK(page)) {
+                    ok = true;
+                    src = cache + (size_t)page * page_stride + (size_t)G * page_size * D + ((size_t)(col / E) * page_size + j % page_size) * E + col % E;
+                }
             }
-            *reinterpret_cast<uint4*>(Vs + jj * VP + ch * 8) = val;
+            copy16_async(Vb + jj * VP + ch * 8, src, ok);
         }
-        __syncthreads();
+        copies_commit();
+    };
+    fetch(0, 0);
+    for (int ti = 0; ti < n_tiles; ++ti) {
+        const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
+        const int j0 = kt * BN;
+        if (ti + 1 < n_tiles) {
+            fetch(ti + 1, (ti + 1) & 1);
+            copies_wait<1>();
+        } else {
+            copies_wait<0>();
+        }
+        __syncthreads();                                                  // tile ti has landed for every thread
+        const __nv_bfloat16* Kt = Ks + (ti & 1) * stage;
+        const __nv_bfloat16* Vt = Vs + (ti & 1) * stage;
 
         // S = Q K^T for this warp's 16 rows and the tile's 64 keys
         float sacc[BN / 8][4];
@@ -128,7 +159,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
             for (int nt = 0; nt < BN / 8; nt += 2) {
                 uint32_t b[4];      // keys nt*8 .. nt*8+15: (b0, b1) of the first eight, (b0, b1) of the next eight
-                ldmatrix_x4(b, Ks + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * DP + k0 + ((lane >> 3) & 1) * 8);
+                ldmatrix_x4(b, Kt + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * DP + k0 + ((lane >> 3) & 1) * 8);
                 mma_bf16(sacc[nt], a, b[0], b[1]);
                 mma_bf16(sacc[nt + 1], a, b[2], b[3]);
             }
@@ -187,11 +218,12 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
             for (int nt = 0; nt < VC / 8; nt += 2) {
                 uint32_t b[4];      // keys kk*16 .. +15 (rows), columns nt*8 .. +15: matrices (k lo, n lo), (k hi, n lo), (k lo, n hi), (k hi, n hi)
-                ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nt * 8 + (lane >> 4) * 8);
+                ldmatrix_x4_trans(b, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nt * 8 + (lane >> 4) * 8);
                 mma_bf16(oacc[nt], pa[kk], b[0], b[1]);
                 mma_bf16(oacc[nt + 1], pa[kk], b[2], b[3]);
             }
         }
+        __syncthreads();                                                  // before the next fetch writes into this buffer's twin's successor
     }
     // normalise and store this chunk's columns of u
     const float inv[2] = {row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f, row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f};
@@ -209,31 +241,46 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 }
 
 // out[t, h, e] = gate[t, h] * sum_g mix[h, g] u[t, g, kv(h) * E + e]      (mix null: u[t, h, ...] alone)
+// One CTA per (token, key/value head c): the H x E block of u that the query heads of c read goes to shared memory
+// once (rows of E consecutive numbers), then a thread per (head of c, channel) takes its sum over g.
 __global__ void __launch_bounds__(128)
 headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ mix, const float* __restrict__ gate,
                        __nv_bfloat16* __restrict__ out, int H, int G, int E) {
-    extern __shared__ float mx[];
+    extern __shared__ float sm[];
     forge::pdl_launch_dependents();
-    if (mix) for (int i = threadIdx.x; i < H * H; i += blockDim.x) mx[i] = mix[i];
+    const int t = blockIdx.x, c = blockIdx.y, GE = G * E, Gq = H / G;
+    float* mx = sm;                     // [Gq][H] rows of mix of this group's heads
+    float* ub = sm + (mix ? Gq * H : 0);     // [H][E]
+    if (mix) for (int i = threadIdx.x; i < Gq * H; i += blockDim.x) mx[i] = mix[(size_t)c * Gq * H + i];
     forge::pdl_wait();
+    const float* ut = u + (size_t)t * H * GE + (size_t)c * E;
+    if (mix) {
+        for (int i = threadIdx.x; i < H * E; i += blockDim.x) ub[i] = ut[(size_t)(i / E) * GE + i % E];
+    }
     __syncthreads();
-    const int t = blockIdx.x, GE = G * E, Gq = H / G;
-    const float* ut = u + (size_t)t * H * GE;
-    for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
-        const int h = i / E, e = i % E, col = (h / Gq) * E + e;
+    for (int i = threadIdx.x; i < Gq * E; i += blockDim.x) {
+        const int hq = i / E, e = i % E, h = c * Gq + hq;
         float a;
         if (mix) {
-            a = 0.f;
-            for (int g = 0; g < H; ++g) a = fmaf(mx[h * H + g], ut[(size_t)g * GE + col], a);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            int g = 0;
+            for (; g + 3 < H; g += 4) {
+                a0 = fmaf(mx[hq * H + g], ub[g * E + e], a0);
+                a1 = fmaf(mx[hq * H + g + 1], ub[(g + 1) * E + e], a1);
+                a2 = fmaf(mx[hq * H + g + 2], ub[(g + 2) * E + e], a2);
+                a3 = fmaf(mx[hq * H + g + 3], ub[(g + 3) * E + e], a3);
+            }
+            for (; g < H; ++g) a0 = fmaf(mx[hq * H + g], ub[g * E + e], a0);
+            a = (a0 + a1) + (a2 + a3);
         } else {
-            a = ut[(size_t)h * GE + col];
+            a = ut[(size_t)h * GE + e];
         }
         if (gate) a *= gate[(size_t)t * H + h];
-        out[(size_t)t * H * E + i] = __float2bfloat16_rn(a);
+        out[((size_t)t * H + h) * E + e] = __float2bfloat16_rn(a);
     }
 }
 
-forge::PerDeviceFlag g_attr_done[3];
+forge::PerDeviceFlag g_attr_done[3], g_combine_done;
 
 template <int VC>
 int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
@@ -275,7 +322,7 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     for (int cand : {128, 256})
         if ((GE + cand - 1) / cand * cand <= (GE + VC - 1) / VC * VC) VC = cand;
     const int chunks = (GE + VC - 1) / VC;
-    const size_t smem = sizeof(__nv_bfloat16) * ((size_t)(BM + BN) * (D + kPad) + (size_t)BN * (VC + kPad));
+    const size_t smem = sizeof(__nv_bfloat16) * ((size_t)(BM + 2 * BN) * (D + kPad) + 2 * (size_t)BN * (VC + kPad));
     const dim3 grid(num_tiles, G, chunks);
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
@@ -284,7 +331,15 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     if (rc != FORGE_OK) return rc;
-    return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T), dim3(128), mix ? sizeof(float) * H * H : 0, stream, 1,
+    const size_t csmem = mix ? sizeof(float) * ((size_t)(H / G) * H + (size_t)H * E) : 0;
+    if (csmem > 160 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_combine: %d heads of %d channels", H, E);
+    bool& cdone = g_combine_done.current();
+    if (!cdone) {
+        cudaError_t e = cudaFuncSetAttribute(headmix_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return forge::check_launch("headmix_combine (shared memory)", e);
+        cdone = true;
+    }
+    return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T, G), dim3(128), csmem, stream, 1,
                                                                 (const float*)u, mix, gate, (__nv_bfloat16*)out, H, G, E));
 }
 

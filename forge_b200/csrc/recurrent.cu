@@ -9,10 +9,10 @@
 //                              n_t = k_t / sqrt(|k_t|^2 + 1e-6),  w_t = exp(-exp(-1/2) sigmoid(x_t + w0)),
 //                              a_t = sigmoid(y_t + a0)               (both terms read the state before the step)
 //
-// One CTA per (request, head) walks the request's tokens of the step in order; thread j owns column j of S
-// (the K numbers that meet value channel j) in registers, so a token costs K multiply-adds per thread and no
-// exchange between threads except the vectors r, k, w (, a) of the token, which are staged in shared memory a few
-// tokens at a time.  The walk is the same whether a request's tokens come in one step or in many: state and sums
+// One CTA per (request, head) walks the request's tokens of the step in order; column j of S (the K numbers that meet
+// value channel j) lives in the registers of four neighbouring threads, so a token costs K/4 multiply-adds per thread,
+// two shuffles, and no other exchange between threads except the vectors r, k, w (, a) of the token, which are staged
+// in shared memory a few tokens at a time.  The walk is the same whether a request's tokens come in one step or in many: state and sums
 // see the same operations in the same order.
 #include "common.cuh"
 
@@ -27,95 +27,150 @@ struct ScanInput {                    // a [T, heads * K] fp32 matrix that may b
 
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+constexpr int kSplit = 4;             // threads that share a column of S (each holds a quarter of its rows)
+
 // MODE 0: decay and bonus; MODE 1: generalized delta rule.
 // x: what the decay is made from (before w0 is added); y: what the removal rate is made from (MODE 1).
 // last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the request's last row is
 // kept as fp32 at state + prev_off (the next step's "previous token").
+//
+// Thread (j, q) = (tid / 4, tid % 4) holds rows q*KMAX/4 .. of column j, so a token is KMAX/4 multiply-adds deep per
+// thread and the four partial sums of a column meet by two shuffles, always in the same order.  The vectors of the next
+// kScanTokens tokens are asked for before the present ones are worked on and go to the other half of the staging buffers.
 template <int KMAX, int MODE, typename TA>
-__global__ void __launch_bounds__(KMAX)
+__global__ void __launch_bounds__(KMAX * kSplit)
 state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y, const float* __restrict__ w0,
                   const float* __restrict__ a0, const float* __restrict__ bonus, float* __restrict__ state, long long state_stride,
                   const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, float* __restrict__ out,
                   const TA* __restrict__ last_in, int W, long long prev_off, int N, int K) {
-    __shared__ float rs[kScanTokens][KMAX], ks[kScanTokens][KMAX], ds[kScanTokens][KMAX], as[MODE == 1 ? kScanTokens : 1][KMAX];
-    __shared__ float us[KMAX], vs[kScanTokens][KMAX];
+    constexpr int RPT = KMAX / kSplit, TPT = kScanTokens / kSplit;      // rows of S, and staged tokens, per thread
+    __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
+    __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][KMAX], us[KMAX];
     forge::pdl_launch_dependents();
-    const int s = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
+    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, j = tid / kSplit, q = tid % kSplit, i0 = q * RPT;
     const bool live = j < K;
     const int col = head * K + j;
     const float w0j = live ? w0[col] : 0.f;
     const float a0j = (MODE == 1 && live) ? a0[col] : 0.f;
-    if (MODE == 0) us[j] = live ? bonus[col] : 0.f;
+    if (MODE == 0 && q == 0) us[j] = live ? bonus[col] : 0.f;
     forge::pdl_wait();
     const int t_lo = q_start[s], t_hi = q_start[s + 1];
     float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * K;
-    float S[KMAX];
+    float S[RPT];
 #pragma unroll
-    for (int i = 0; i < KMAX; ++i) S[i] = (live && i < K) ? S_g[(size_t)i * K + j] : 0.f;
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && i0 + ii < K) ? S_g[(size_t)(i0 + ii) * K + j] : 0.f;
 
-    for (int tb = t_lo; tb < t_hi; tb += kScanTokens) {
-        const int n = min(kScanTokens, t_hi - tb);
-        __syncthreads();                                   // the tokens before are done with the staged vectors
+    // this thread stages channel j of tokens q*TPT .. q*TPT+TPT-1 of a group
+    float in_r[TPT], in_k[TPT], in_v[TPT], in_x[TPT], in_y[TPT];
+    auto ask = [&](int tb) {
 #pragma unroll
-        for (int tt = 0; tt < kScanTokens; ++tt) {
-            float rj = 0.f, kj = 0.f, dj = 0.f, aj = 0.f, vj = 0.f;
-            if (tt < n && live) {
-                const size_t t = (size_t)(tb + tt);
-                rj = r.p[t * r.ld + col];
-                kj = k.p[t * k.ld + col];
-                vj = v.p[t * v.ld + col];
-                const float xj = x.p[t * x.ld + col] + w0j;
-                if (MODE == 0) dj = expf(-expf(xj));
-                else {
-                    dj = expf(-0.6065306597126334f * sigmoidf(xj));
-                    aj = sigmoidf(y.p[t * y.ld + col] + a0j);
-                }
-            }
-            rs[tt][j] = rj;
-            ks[tt][j] = kj;
-            ds[tt][j] = dj;
-            if (MODE == 1) as[tt][j] = aj;
-            vs[tt][j] = vj;
+        for (int u = 0; u < TPT; ++u) {
+            const int t = tb + q * TPT + u;
+            const bool ok = live && t < t_hi;
+            in_r[u] = ok ? r.p[(size_t)t * r.ld + col] : 0.f;
+            in_k[u] = ok ? k.p[(size_t)t * k.ld + col] : 0.f;
+            in_v[u] = ok ? v.p[(size_t)t * v.ld + col] : 0.f;
+            in_x[u] = ok ? x.p[(size_t)t * x.ld + col] : 0.f;
+            in_y[u] = (MODE == 1 && ok) ? y.p[(size_t)t * y.ld + col] : 0.f;
         }
-        __syncthreads();
+    };
+    auto put = [&](int buf, int tb) {
+#pragma unroll
+        for (int u = 0; u < TPT; ++u) {
+            const int tt = q * TPT + u;
+            const bool ok = live && tb + tt < t_hi;
+            rs[buf][tt][j] = in_r[u];
+            ks[buf][tt][j] = in_k[u];
+            vs[buf][tt][j] = in_v[u];
+            if (MODE == 0) {
+                ds[buf][tt][j] = ok ? expf(-expf(in_x[u] + w0j)) : 0.f;
+            } else {
+                ds[buf][tt][j] = ok ? expf(-0.6065306597126334f * sigmoidf(in_x[u] + w0j)) : 0.f;
+                as[buf][tt][j] = ok ? sigmoidf(in_y[u] + a0j) : 0.f;
+            }
+        }
+    };
+    ask(t_lo);
+    put(0, t_lo);
+    __syncthreads();
+    int buf = 0;
+    for (int tb = t_lo; tb < t_hi; tb += kScanTokens, buf ^= 1) {
+        const int n = min(kScanTokens, t_hi - tb);
+        const bool more = tb + kScanTokens < t_hi;
+        if (more) ask(tb + kScanTokens);
 #pragma unroll 1
         for (int tt = 0; tt < n; ++tt) {
-            const float vj = vs[tt][j];
-            float acc = 0.f;
+            const float vj = vs[buf][tt][j];
+            const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][i0]);
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][i0]);
+            const float4* d4 = reinterpret_cast<const float4*>(&ds[buf][tt][i0]);
+            float acc0 = 0.f, acc1 = 0.f;
             if (MODE == 0) {
+                const float4* u4 = reinterpret_cast<const float4*>(&us[i0]);
 #pragma unroll
-                for (int i = 0; i < KMAX; ++i) {
-                    const float kv = ks[tt][i] * vj;
-                    acc = fmaf(rs[tt][i], fmaf(us[i], kv, S[i]), acc);
-                    S[i] = fmaf(ds[tt][i], S[i], kv);
+                for (int c4 = 0; c4 < RPT / 4; ++c4) {
+                    const float4 rr = r4[c4], kk = k4[c4], dd = d4[c4], uu = u4[c4];
+                    const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+                    const float dv[4] = {dd.x, dd.y, dd.z, dd.w}, uv[4] = {uu.x, uu.y, uu.z, uu.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int ii = c4 * 4 + e;
+                        const float kv = kv4[e] * vj;
+                        if (e & 1) acc1 = fmaf(rv[e], fmaf(uv[e], kv, S[ii]), acc1);
+                        else acc0 = fmaf(rv[e], fmaf(uv[e], kv, S[ii]), acc0);
+                        S[ii] = fmaf(dv[e], S[ii], kv);
+                    }
                 }
             } else {
-                float held = 0.f, kk = 0.f;                // k^T S (this column) and |k|^2
+                const float4* a4 = reinterpret_cast<const float4*>(&as[buf][tt][i0]);
+                float held = 0.f, kk2 = 0.f;               // this thread's share of k^T S (its column) and of |k|^2
 #pragma unroll
-                for (int i = 0; i < KMAX; ++i) {
-                    held = fmaf(ks[tt][i], S[i], held);
-                    kk = fmaf(ks[tt][i], ks[tt][i], kk);
+                for (int c4 = 0; c4 < RPT / 4; ++c4) {
+                    const float4 kk = k4[c4];
+                    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        held = fmaf(kv4[e], S[c4 * 4 + e], held);
+                        kk2 = fmaf(kv4[e], kv4[e], kk2);
+                    }
                 }
+                held += __shfl_xor_sync(0xffffffffu, held, 1);
+                kk2 += __shfl_xor_sync(0xffffffffu, kk2, 1);
+                held += __shfl_xor_sync(0xffffffffu, held, 2);
+                kk2 += __shfl_xor_sync(0xffffffffu, kk2, 2);
                 // (a * n)(n^T S) = a_i k_i (k^T S) / (|k|^2 + 1e-6): the two roots of the unit key multiply out
-                const float share = held / (kk + 1e-6f);
+                const float share = held / (kk2 + 1e-6f);
 #pragma unroll
-                for (int i = 0; i < KMAX; ++i) {
-                    S[i] = fmaf(ds[tt][i], S[i], ks[tt][i] * (vj - as[tt][i] * share));
-                    acc = fmaf(rs[tt][i], S[i], acc);
+                for (int c4 = 0; c4 < RPT / 4; ++c4) {
+                    const float4 rr = r4[c4], kk = k4[c4], dd = d4[c4], aa = a4[c4];
+                    const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+                    const float dv[4] = {dd.x, dd.y, dd.z, dd.w}, av[4] = {aa.x, aa.y, aa.z, aa.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int ii = c4 * 4 + e;
+                        S[ii] = fmaf(dv[e], S[ii], kv4[e] * (vj - av[e] * share));
+                        if (e & 1) acc1 = fmaf(rv[e], S[ii], acc1);
+                        else acc0 = fmaf(rv[e], S[ii], acc0);
+                    }
                 }
             }
-            if (live) out[(size_t)(tb + tt) * N * K + col] = acc;
+            float acc = acc0 + acc1;
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (live && q == 0) out[(size_t)(tb + tt) * N * K + col] = acc;
         }
+        if (more) put(buf ^ 1, tb + kScanTokens);
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < KMAX; ++i)
-            if (i < K) S_g[(size_t)i * K + j] = S[i];
+        for (int ii = 0; ii < RPT; ++ii)
+            if (i0 + ii < K) S_g[(size_t)(i0 + ii) * K + j] = S[ii];
     }
     if (MODE == 0 && last_in != nullptr && t_hi > t_lo) {
         float* prev = state + (size_t)slots[s] * state_stride + prev_off;
         const TA* row = last_in + (size_t)(t_hi - 1) * W;
-        for (int c = head * KMAX + j; c < W; c += N * KMAX) prev[c] = forge::to_float(row[c]);
+        for (int c = head * (KMAX * kSplit) + tid; c < W; c += N * KMAX * kSplit) prev[c] = forge::to_float(row[c]);
     }
 }
 
@@ -178,7 +233,7 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
                         const int32_t* slots, float* out, const TA* last_in, int W, long long prev_off, int N, int K) {
 #define FORGE_SCAN_CASE(KM)                                                                                              \
     case KM:                                                                                                             \
-        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(KM), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
+        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(KM * kSplit), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
                              state, stride, q_start, slots, out, last_in, W, prev_off, N, K);
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
