@@ -42,6 +42,11 @@ __device__ __forceinline__ void copy16_async(void* dst, const void* src, bool ok
 __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ float ex2(float x) {          // 2^x, relative error 2^-22; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -72,6 +77,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int stage = BN * (DP + VP);                                     // elements of one buffer: a key tile and a value tile
     __nv_bfloat16* Ks = Qs + BM * DP;                                     // 2 x [BN][D + 8]
     __nv_bfloat16* Vs = Ks + BN * DP;                                     // 2 x [BN][VC + 8], each behind its key tile
+    __shared__ int voff[VC / 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
@@ -100,38 +106,39 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int n_tiles = kept_tiles + (last_tile - first_win_tile + 1);
     const float sl2 = scale * 1.4426950408889634f;                        // scores in units of log2(e)
     const int vchunks = VC >> 3;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    if (tid < vchunks) {
+        const int col = v0 + tid * 8;
+        voff[tid] = col < GE ? G * page_size * D + (col / E) * page_size * E + col % E : -1;
+    }
+    __syncthreads();
 
     // key and value tiles go through two buffers: tile ti + 1 is on its way while tile ti is worked on
+    // Two threads a key row: one look into the block table per thread and tile; what depends on the column alone (which
+    // key/value head a 16-byte piece of a value row belongs to, and where in it) was worked out once, into voff.
+    const int frow = tid >> 1, fpar = tid & 1;
     auto fetch = [&](int ti, int buf) {
         const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
-        const int j0 = kt * BN;
-        __nv_bfloat16* Kb = Ks + buf * stage;
-        __nv_bfloat16* Vb = Vs + buf * stage;
-        for (int i = tid; i < BN * dchunks; i += kThreads) {
-            const int jj = i / dchunks, ch = i % dchunks, j = j0 + jj;
-            const __nv_bfloat16* src = cache;
-            bool ok = false;
-            if (j <= pos_last) {
-                const int page = table[j / page_size];
-                if (page >= 0 && FORGE_PAGE_OK(page)) {
-                    ok = true;
-                    src = cache + (size_t)page * page_stride + ((size_t)c * page_size + j % page_size) * D + ch * 8;
-                }
+        const int j = kt * BN + frow;
+        __nv_bfloat16* Kb = Ks + buf * stage + frow * DP;
+        __nv_bfloat16* Vb = Vs + buf * stage + frow * VP;
+        const __nv_bfloat16* page_base = cache;
+        bool ok = false;
+        if (j <= pos_last) {
+            const int page = table[j >> page_shift];
+            if (page >= 0 && FORGE_PAGE_OK(page)) {
+                ok = true;
+                page_base = cache + (size_t)page * page_stride;
             }
-            copy16_async(Kb + jj * DP + ch * 8, src, ok);
         }
-        for (int i = tid; i < BN * vchunks; i += kThreads) {
-            const int jj = i / vchunks, ch = i % vchunks, j = j0 + jj, col = v0 + ch * 8;
-            const __nv_bfloat16* src = cache;
-            bool ok = false;
-            if (j <= pos_last && col < GE) {
-                const int page = table[j / page_size];
-                if (page >= 0 && FORGE_PAGE_OK(page)) {
-                    ok = true;
-                    src = cache + (size_t)page * page_stride + (size_t)G * page_size * D + ((size_t)(col / E) * page_size + j % page_size) * E + col % E;
-                }
-            }
-            copy16_async(Vb + jj * VP + ch * 8, src, ok);
+        const int off = j & (page_size - 1);
+        const __nv_bfloat16* ksrc = page_base + ((size_t)c * page_size + off) * D;
+        for (int ch = fpar; ch < dchunks; ch += 2) copy16_async(Kb + ch * 8, ok ? ksrc + ch * 8 : cache, ok);
+        const __nv_bfloat16* vsrc = page_base + (size_t)off * E;
+        for (int ch = fpar; ch < vchunks; ch += 2) {
+            const int o = voff[ch];
+            copy16_async(Vb + ch * 8, (ok && o >= 0) ? vsrc + o : cache, ok && o >= 0);
         }
         copies_commit();
     };
@@ -164,18 +171,30 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                 mma_bf16(sacc[nt + 1], a, b[2], b[3]);
             }
         }
-        // scale, mask, and the tile's maximum per row
+        // scale, mask, and the tile's maximum per row.  A tile that every row of the CTA sees whole needs no mask.
+        const bool whole = rows == BM && j0 + BN - 1 <= pos0 && (window <= 0 || pos_last - j0 < window || j0 + BN - 1 < keep_first);
         float tmax[2] = {-INFINITY, -INFINITY};
+        if (whole) {
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; ++nt) {
+            for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const bool hi = e >= 2;
-                const bool ok = (hi ? live_hi : live_lo) && visible(hi ? pos_hi : pos_lo, j, window, keep_first);
-                const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
-                sacc[nt][e] = s;
-                tmax[hi] = fmaxf(tmax[hi], s);
+                for (int e = 0; e < 4; ++e) {
+                    sacc[nt][e] *= sl2;
+                    tmax[e >> 1] = fmaxf(tmax[e >> 1], sacc[nt][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool hi = e >= 2;
+                    const bool ok = (hi ? live_hi : live_lo) && visible(hi ? pos_hi : pos_lo, j, window, keep_first);
+                    const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
+                    sacc[nt][e] = s;
+                    tmax[hi] = fmaxf(tmax[hi], s);
+                }
             }
         }
         float alpha[2], base[2];
@@ -185,15 +204,15 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
             const float m_new = fmaxf(row_m[h], tmax[h]);
             base[h] = m_new == -INFINITY ? 0.f : m_new;                   // a row that has seen nothing yet
-            alpha[h] = exp2f(row_m[h] - base[h]);                         // exp2(-inf) = 0
+            alpha[h] = ex2(row_m[h] - base[h]);                         // exp2(-inf) = 0
             row_m[h] = m_new;
         }
         float tsum[2] = {0.f, 0.f};
         uint32_t pa[BN / 16][4];                                          // P as the A operand, 16 keys per k-step
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
-            const float p0 = exp2f(sacc[nt][0] - base[0]), p1 = exp2f(sacc[nt][1] - base[0]);
-            const float p2 = exp2f(sacc[nt][2] - base[1]), p3 = exp2f(sacc[nt][3] - base[1]);
+            const float p0 = ex2(sacc[nt][0] - base[0]), p1 = ex2(sacc[nt][1] - base[0]);
+            const float p2 = ex2(sacc[nt][2] - base[1]), p3 = ex2(sacc[nt][3] - base[1]);
             tsum[0] += p0 + p1;
             tsum[1] += p2 + p3;
             pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
@@ -300,9 +319,10 @@ int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __n
 }  // namespace
 
 // 1 if the tensor-core kernels take these sizes: key heads of a multiple of 16 channels up to 128, value heads of a
-// multiple of 8 channels, at most 64 query heads per key/value head, at most 96 heads (the exchange matrix in shared memory).
-extern "C" int forge_headmix_mma_supports(int H, int G, int D, int E) {
-    return (H > 0 && G > 0 && H % G == 0 && H / G <= BM && H <= 96 && D % 16 == 0 && D >= 16 && D <= 128 && E % 8 == 0 && E > 0) ? 1 : 0;
+// multiple of 8 channels, at most 64 query heads per key/value head, at most 96 heads (the exchange matrix in shared memory),
+// pages of a power of two tokens.
+extern "C" int forge_headmix_mma_supports(int H, int G, int D, int E, int page_size) {
+    return (page_size > 0 && (page_size & (page_size - 1)) == 0 && H > 0 && G > 0 && H % G == 0 && H / G <= BM && H <= 96 && D % 16 == 0 && D >= 16 && D <= 128 && E % 8 == 0 && E > 0) ? 1 : 0;
 }
 
 // q bf16 [T, H*D]; u fp32 [T, H, G*E] (scratch); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive tokens of one
@@ -313,7 +333,7 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
                                            const float* gate, float* u, void* out, int T, int num_tiles, int H, int G, int D, int E,
                                            int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale,
                                            cudaStream_t stream) {
-    if (!forge_headmix_mma_supports(H, G, D, E)) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_attention_mma: H=%d G=%d D=%d E=%d", H, G, D, E);
+    if (!forge_headmix_mma_supports(H, G, D, E, page_size)) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_attention_mma: H=%d G=%d D=%d E=%d", H, G, D, E);
     if (T < 0 || num_tiles < 0 || page_size <= 0 || max_pages <= 0 || keep_first < 0 || (tile_t0 == nullptr) != (tile_n == nullptr))
         return forge::fail(FORGE_ERR_ARG, "headmix_attention_mma: bad arguments");
     if (T == 0 || num_tiles == 0) return FORGE_OK;

@@ -9,10 +9,10 @@
 //                              n_t = k_t / sqrt(|k_t|^2 + 1e-6),  w_t = exp(-exp(-1/2) sigmoid(x_t + w0)),
 //                              a_t = sigmoid(y_t + a0)               (both terms read the state before the step)
 //
-// One CTA per (request, head) walks the request's tokens of the step in order; column j of S (the K numbers that meet
-// value channel j) lives in the registers of four neighbouring threads, so a token costs K/4 multiply-adds per thread,
-// two shuffles, and no other exchange between threads except the vectors r, k, w (, a) of the token, which are staged
-// in shared memory a few tokens at a time.  The walk is the same whether a request's tokens come in one step or in many: state and sums
+// A CTA per (request, head, 16 columns of S) walks the request's tokens of the step in order; column j of S (the K numbers
+// that meet value channel j) lives in the registers of eight neighbouring threads, so a token costs K/8 multiply-adds per
+// thread, three shuffles, and no other exchange between threads except the vectors r, k, w (, a) of the token, which are
+// staged in shared memory a few tokens at a time.  The walk is the same whether a request's tokens come in one step or in many: state and sums
 // see the same operations in the same order.
 #include "common.cuh"
 
@@ -27,32 +27,44 @@ struct ScanInput {                    // a [T, heads * K] fp32 matrix that may b
 
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-constexpr int kSplit = 4;             // threads that share a column of S (each holds a quarter of its rows)
+constexpr int kSplit = 8;             // threads that share a column of S (each holds an eighth of its rows)
+constexpr int kCols = 16;             // columns of S per CTA
+constexpr int kScanThreads = kSplit * kCols;
 
 // MODE 0: decay and bonus; MODE 1: generalized delta rule.
 // x: what the decay is made from (before w0 is added); y: what the removal rate is made from (MODE 1).
 // last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the request's last row is
 // kept as fp32 at state + prev_off (the next step's "previous token").
 //
-// Thread (j, q) = (tid / 4, tid % 4) holds rows q*KMAX/4 .. of column j, so a token is KMAX/4 multiply-adds deep per
-// thread and the four partial sums of a column meet by two shuffles, always in the same order.  The vectors of the next
-// kScanTokens tokens are asked for before the present ones are worked on and go to the other half of the staging buffers.
+// A CTA has 16 columns of one head's S; thread (jl, q) = (tid / 8, tid % 8) holds rows q*KMAX/8 .. of column
+// blockIdx.z*16 + jl, so a token is KMAX/8 multiply-adds deep per thread and the eight partial sums of a column meet by
+// three shuffles, always in the same order.  A head's columns are spread over K/16 CTAs so that one long request keeps
+// many SMs busy, each with one warp per scheduler.  The vectors of the next kScanTokens tokens are asked for before the
+// present ones are worked on and go to the other half of the staging buffers.
 template <int KMAX, int MODE, typename TA>
-__global__ void __launch_bounds__(KMAX * kSplit)
+__global__ void __launch_bounds__(kScanThreads)
 state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y, const float* __restrict__ w0,
                   const float* __restrict__ a0, const float* __restrict__ bonus, float* __restrict__ state, long long state_stride,
                   const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, float* __restrict__ out,
                   const TA* __restrict__ last_in, int W, long long prev_off, int N, int K) {
-    constexpr int RPT = KMAX / kSplit, TPT = kScanTokens / kSplit;      // rows of S, and staged tokens, per thread
+    constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
+    constexpr int SPT = kScanTokens * KMAX / kScanThreads;              // staged (token, channel) pairs per thread
     __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
-    __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][KMAX], us[KMAX];
+    __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
     forge::pdl_launch_dependents();
-    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, j = tid / kSplit, q = tid % kSplit, i0 = q * RPT;
+    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, jl = tid / kSplit, q = tid % kSplit, i0 = q * RPT;
+    const int j = blockIdx.z * kCols + jl;
     const bool live = j < K;
     const int col = head * K + j;
-    const float w0j = live ? w0[col] : 0.f;
-    const float a0j = (MODE == 1 && live) ? a0[col] : 0.f;
-    if (MODE == 0 && q == 0) us[j] = live ? bonus[col] : 0.f;
+    // staging: pair p = tid + u * threads -> token p / KMAX, channel p % KMAX (channels of a token side by side)
+    float w0c[SPT], a0c[SPT];
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) {
+        const int ch = (tid + u * kScanThreads) % KMAX;
+        w0c[u] = ch < K ? w0[head * K + ch] : 0.f;
+        a0c[u] = (MODE == 1 && ch < K) ? a0[head * K + ch] : 0.f;
+    }
+    if (MODE == 0) for (int i = tid; i < KMAX; i += kScanThreads) us[i] = i < K ? bonus[head * K + i] : 0.f;
     forge::pdl_wait();
     const int t_lo = q_start[s], t_hi = q_start[s + 1];
     float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * K;
@@ -60,35 +72,36 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && i0 + ii < K) ? S_g[(size_t)(i0 + ii) * K + j] : 0.f;
 
-    // this thread stages channel j of tokens q*TPT .. q*TPT+TPT-1 of a group
-    float in_r[TPT], in_k[TPT], in_v[TPT], in_x[TPT], in_y[TPT];
+    float in_r[SPT], in_k[SPT], in_x[SPT], in_y[SPT], in_v;
     auto ask = [&](int tb) {
 #pragma unroll
-        for (int u = 0; u < TPT; ++u) {
-            const int t = tb + q * TPT + u;
-            const bool ok = live && t < t_hi;
-            in_r[u] = ok ? r.p[(size_t)t * r.ld + col] : 0.f;
-            in_k[u] = ok ? k.p[(size_t)t * k.ld + col] : 0.f;
-            in_v[u] = ok ? v.p[(size_t)t * v.ld + col] : 0.f;
-            in_x[u] = ok ? x.p[(size_t)t * x.ld + col] : 0.f;
-            in_y[u] = (MODE == 1 && ok) ? y.p[(size_t)t * y.ld + col] : 0.f;
+        for (int u = 0; u < SPT; ++u) {
+            const int p = tid + u * kScanThreads, t = tb + p / KMAX, ch = p % KMAX;
+            const bool ok = ch < K && t < t_hi;
+            const size_t c = (size_t)head * K + ch;
+            in_r[u] = ok ? r.p[(size_t)t * r.ld + c] : 0.f;
+            in_k[u] = ok ? k.p[(size_t)t * k.ld + c] : 0.f;
+            in_x[u] = ok ? x.p[(size_t)t * x.ld + c] : 0.f;
+            in_y[u] = (MODE == 1 && ok) ? y.p[(size_t)t * y.ld + c] : 0.f;
         }
+        const int t = tb + tid / kCols, jc = blockIdx.z * kCols + tid % kCols;          // values: this CTA's columns only
+        in_v = (jc < K && t < t_hi) ? v.p[(size_t)t * v.ld + head * K + jc] : 0.f;
     };
     auto put = [&](int buf, int tb) {
 #pragma unroll
-        for (int u = 0; u < TPT; ++u) {
-            const int tt = q * TPT + u;
-            const bool ok = live && tb + tt < t_hi;
-            rs[buf][tt][j] = in_r[u];
-            ks[buf][tt][j] = in_k[u];
-            vs[buf][tt][j] = in_v[u];
+        for (int u = 0; u < SPT; ++u) {
+            const int p = tid + u * kScanThreads, tt = p / KMAX, ch = p % KMAX;
+            const bool ok = ch < K && tb + tt < t_hi;
+            rs[buf][tt][ch] = in_r[u];
+            ks[buf][tt][ch] = in_k[u];
             if (MODE == 0) {
-                ds[buf][tt][j] = ok ? expf(-expf(in_x[u] + w0j)) : 0.f;
+                ds[buf][tt][ch] = ok ? expf(-expf(in_x[u] + w0c[u])) : 0.f;
             } else {
-                ds[buf][tt][j] = ok ? expf(-0.6065306597126334f * sigmoidf(in_x[u] + w0j)) : 0.f;
-                as[buf][tt][j] = ok ? sigmoidf(in_y[u] + a0j) : 0.f;
+                ds[buf][tt][ch] = ok ? expf(-0.6065306597126334f * sigmoidf(in_x[u] + w0c[u])) : 0.f;
+                as[buf][tt][ch] = ok ? sigmoidf(in_y[u] + a0c[u]) : 0.f;
             }
         }
+        vs[buf][tid / kCols][tid % kCols] = in_v;
     };
     ask(t_lo);
     put(0, t_lo);
@@ -98,9 +111,9 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
         const int n = min(kScanTokens, t_hi - tb);
         const bool more = tb + kScanTokens < t_hi;
         if (more) ask(tb + kScanTokens);
-#pragma unroll 1
+#pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
-            const float vj = vs[buf][tt][j];
+            const float vj = vs[buf][tt][jl];
             const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][i0]);
             const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][i0]);
             const float4* d4 = reinterpret_cast<const float4*>(&ds[buf][tt][i0]);
@@ -134,10 +147,11 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
                         kk2 = fmaf(kv4[e], kv4[e], kk2);
                     }
                 }
-                held += __shfl_xor_sync(0xffffffffu, held, 1);
-                kk2 += __shfl_xor_sync(0xffffffffu, kk2, 1);
-                held += __shfl_xor_sync(0xffffffffu, held, 2);
-                kk2 += __shfl_xor_sync(0xffffffffu, kk2, 2);
+#pragma unroll
+                for (int o = 1; o < kSplit; o <<= 1) {
+                    held += __shfl_xor_sync(0xffffffffu, held, o);
+                    kk2 += __shfl_xor_sync(0xffffffffu, kk2, o);
+                }
                 // (a * n)(n^T S) = a_i k_i (k^T S) / (|k|^2 + 1e-6): the two roots of the unit key multiply out
                 const float share = held / (kk2 + 1e-6f);
 #pragma unroll
@@ -155,8 +169,8 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
                 }
             }
             float acc = acc0 + acc1;
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+#pragma unroll
+            for (int o = 1; o < kSplit; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && q == 0) out[(size_t)(tb + tt) * N * K + col] = acc;
         }
         if (more) put(buf ^ 1, tb + kScanTokens);
@@ -170,7 +184,8 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
     if (MODE == 0 && last_in != nullptr && t_hi > t_lo) {
         float* prev = state + (size_t)slots[s] * state_stride + prev_off;
         const TA* row = last_in + (size_t)(t_hi - 1) * W;
-        for (int c = head * (KMAX * kSplit) + tid; c < W; c += N * KMAX * kSplit) prev[c] = forge::to_float(row[c]);
+        const int ctas = N * gridDim.z;
+        for (int c = (head * gridDim.z + blockIdx.z) * kScanThreads + tid; c < W; c += ctas * kScanThreads) prev[c] = forge::to_float(row[c]);
     }
 }
 
@@ -233,7 +248,7 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
                         const int32_t* slots, float* out, const TA* last_in, int W, long long prev_off, int N, int K) {
 #define FORGE_SCAN_CASE(KM)                                                                                              \
     case KM:                                                                                                             \
-        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(KM * kSplit), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
+        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
                              state, stride, q_start, slots, out, last_in, W, prev_off, N, K);
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
@@ -261,7 +276,7 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
     if (mode == 1 && (!y || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs the removal rate");
     if (S == 0) return FORGE_OK;
     const int kmax = (K + 31) / 32 * 32;
-    const dim3 grid(S, N);
+    const dim3 grid(S, N, (K + kCols - 1) / kCols);
     ScanInput R{r, ld_r}, Kk{k, ld_k}, V{v, ld_v}, X{x, ld_x}, Y{y, ld_y};
     cudaError_t e;
     if (mode == 1) {

@@ -61,7 +61,7 @@ _SIGNATURES = {
     "mixers": {
         "forge_headmix_prepare": [_P, _I] + [_P] * 9 + [_I] * 8 + [_LL, _I, _P],
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
-        "forge_headmix_mma_supports": [_I, _I, _I, _I],
+        "forge_headmix_mma_supports": [_I, _I, _I, _I, _I],
         "forge_headmix_attention_mma": [_P] * 11 + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -749,7 +749,7 @@ def headmix_attention(q, cache, group_batch, batch, H, G, D, E, page_size, scale
     applied to the values of each head's kv head, times ``gate`` fp32 [T, H] (None: no gate).  Returns [T, H*E] in q's type."""
     lib = library("mixers")
     T = q.shape[0]
-    if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_headmix_mma_supports.fn(H, G, D, E):
+    if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_headmix_mma_supports.fn(H, G, D, E, page_size):
         # tensor cores: one pass per head over all key/value heads' values, then the exchange between heads
         t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
         u = new_tensor((T, H, G * E), torch.float32, q.device)
