@@ -31,98 +31,114 @@ constexpr int kSplit = 8;             // threads that share a column of S (each 
 constexpr int kCols = 16;             // columns of S per CTA
 constexpr int kScanThreads = kSplit * kCols;
 
-// MODE 0: decay and bonus; MODE 1: generalized delta rule.
-// x: what the decay is made from (before w0 is added); y: what the removal rate is made from (MODE 1).
-// last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the request's last row is
-// kept as fp32 at state + prev_off (the next step's "previous token").
+// What the recurrence multiplies with, made in place from what the projections gave, for all tokens at once:
+//   MODE 0: x <- exp(-exp(x + w0));   MODE 1: x <- exp(-exp(-1/2) sigmoid(x + w0)),  y <- sigmoid(y + a0)
+template <int MODE>
+__global__ void scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld_y, const float* __restrict__ w0,
+                                  const float* __restrict__ a0, int T, int NK) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * NK) return;
+    const size_t t = i / NK;
+    const int c = (int)(i % NK);
+    float* px = x + t * ld_x + c;
+    if (MODE == 0) {
+        *px = expf(-expf(*px + w0[c]));
+    } else {
+        *px = expf(-0.6065306597126334f * sigmoidf(*px + w0[c]));
+        float* py = y + t * ld_y + c;
+        *py = sigmoidf(*py + a0[c]);
+    }
+}
+
+__device__ __forceinline__ void stage_async(float* dst, const float* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    if (bytes == 16) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// MODE 0: decay and bonus; MODE 1: generalized delta rule.  d: the decays, a: the removal rates (MODE 1), both ready made
+// (scan_gates_kernel).  last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the
+// request's last row is kept as fp32 at state + prev_off (the next step's "previous token").
 //
-// A CTA has 16 columns of one head's S; thread (jl, q) = (tid / 8, tid % 8) holds rows q*KMAX/8 .. of column
-// blockIdx.z*16 + jl, so a token is KMAX/8 multiply-adds deep per thread and the eight partial sums of a column meet by
-// three shuffles, always in the same order.  A head's columns are spread over K/16 CTAs so that one long request keeps
-// many SMs busy, each with one warp per scheduler.  The vectors of the next kScanTokens tokens are asked for before the
-// present ones are worked on and go to the other half of the staging buffers.
+// A CTA has 16 columns of one head's S; thread (jl, q) = (tid / 8, tid % 8) holds the rows (4m + e) with m % 8 == q of
+// column blockIdx.z*16 + jl (so the eight threads of a column read neighbouring 16-byte pieces of a staged vector), a
+// token is KMAX/8 multiply-adds deep per thread and the eight partial sums of a column meet by three shuffles, always
+// in the same order.  A head's columns are spread over K/16 CTAs so that one long request keeps many SMs busy, each
+// with one warp per scheduler.  The vectors of the next kScanTokens tokens are copied into the other half of the staging
+// buffers (cp.async, no stop in registers) while the present ones are worked on.
 template <int KMAX, int MODE, typename TA>
 __global__ void __launch_bounds__(kScanThreads)
-state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y, const float* __restrict__ w0,
-                  const float* __restrict__ a0, const float* __restrict__ bonus, float* __restrict__ state, long long state_stride,
-                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, float* __restrict__ out,
-                  const TA* __restrict__ last_in, int W, long long prev_off, int N, int K) {
+state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a, const float* __restrict__ bonus,
+                  float* __restrict__ state, long long state_stride, const int32_t* __restrict__ q_start,
+                  const int32_t* __restrict__ slots, float* __restrict__ out, const TA* __restrict__ last_in, int W,
+                  long long prev_off, int N, int K, int vec) {
     constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
-    constexpr int SPT = kScanTokens * KMAX / kScanThreads;              // staged (token, channel) pairs per thread
     __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
     __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
     forge::pdl_launch_dependents();
-    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, jl = tid / kSplit, q = tid % kSplit, i0 = q * RPT;
+    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, jl = tid / kSplit, q = tid % kSplit;
     const int j = blockIdx.z * kCols + jl;
     const bool live = j < K;
     const int col = head * K + j;
-    // staging: pair p = tid + u * threads -> token p / KMAX, channel p % KMAX (channels of a token side by side)
-    float w0c[SPT], a0c[SPT];
-#pragma unroll
-    for (int u = 0; u < SPT; ++u) {
-        const int ch = (tid + u * kScanThreads) % KMAX;
-        w0c[u] = ch < K ? w0[head * K + ch] : 0.f;
-        a0c[u] = (MODE == 1 && ch < K) ? a0[head * K + ch] : 0.f;
+    // channels beyond K stay zero in every staged vector: the copies never touch them
+    for (int i = tid; i < 2 * kScanTokens * KMAX; i += kScanThreads) {
+        (&rs[0][0][0])[i] = 0.f;
+        (&ks[0][0][0])[i] = 0.f;
+        (&ds[0][0][0])[i] = 0.f;
+        if (MODE == 1) (&as[0][0][0])[i] = 0.f;
     }
-    if (MODE == 0) for (int i = tid; i < KMAX; i += kScanThreads) us[i] = i < K ? bonus[head * K + i] : 0.f;
+    for (int i = tid; i < 2 * kScanTokens * kCols; i += kScanThreads) (&vs[0][0][0])[i] = 0.f;
+    for (int i = tid; i < KMAX; i += kScanThreads) us[i] = (MODE == 0 && i < K) ? bonus[head * K + i] : 0.f;
+    __syncthreads();
     forge::pdl_wait();
     const int t_lo = q_start[s], t_hi = q_start[s + 1];
     float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * K;
+    // row of S that this thread's register ii holds
+    auto row_of = [&](int ii) { return ((ii >> 2) * kSplit + q) * 4 + (ii & 3); };
     float S[RPT];
 #pragma unroll
-    for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && i0 + ii < K) ? S_g[(size_t)(i0 + ii) * K + j] : 0.f;
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && row_of(ii) < K) ? S_g[(size_t)row_of(ii) * K + j] : 0.f;
 
-    float in_r[SPT], in_k[SPT], in_x[SPT], in_y[SPT], in_v;
-    auto ask = [&](int tb) {
-#pragma unroll
-        for (int u = 0; u < SPT; ++u) {
-            const int p = tid + u * kScanThreads, t = tb + p / KMAX, ch = p % KMAX;
-            const bool ok = ch < K && t < t_hi;
-            const size_t c = (size_t)head * K + ch;
-            in_r[u] = ok ? r.p[(size_t)t * r.ld + c] : 0.f;
-            in_k[u] = ok ? k.p[(size_t)t * k.ld + c] : 0.f;
-            in_x[u] = ok ? x.p[(size_t)t * x.ld + c] : 0.f;
-            in_y[u] = (MODE == 1 && ok) ? y.p[(size_t)t * y.ld + c] : 0.f;
+    const int piece = vec ? 4 : 1, pieces = K / piece;                   // a staged vector in pieces of 16 or 4 bytes
+    auto fetch = [&](int buf, int tb) {
+        const int n = min(kScanTokens, t_hi - tb);
+        for (int p = tid; p < n * pieces; p += kScanThreads) {
+            const int tt = p / pieces, ch = (p % pieces) * piece;
+            const size_t t = (size_t)(tb + tt), c = (size_t)head * K + ch;
+            stage_async(&rs[buf][tt][ch], r.p + t * r.ld + c, piece * 4);
+            stage_async(&ks[buf][tt][ch], k.p + t * k.ld + c, piece * 4);
+            stage_async(&ds[buf][tt][ch], d.p + t * d.ld + c, piece * 4);
+            if (MODE == 1) stage_async(&as[buf][tt][ch], a.p + t * a.ld + c, piece * 4);
         }
-        const int t = tb + tid / kCols, jc = blockIdx.z * kCols + tid % kCols;          // values: this CTA's columns only
-        in_v = (jc < K && t < t_hi) ? v.p[(size_t)t * v.ld + head * K + jc] : 0.f;
+        const int tt = tid / kCols, jc = blockIdx.z * kCols + tid % kCols;              // values: this CTA's columns only
+        if (tt < n && jc < K) stage_async(&vs[buf][tt][tid % kCols], v.p + (size_t)(tb + tt) * v.ld + head * K + jc, 4);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto put = [&](int buf, int tb) {
-#pragma unroll
-        for (int u = 0; u < SPT; ++u) {
-            const int p = tid + u * kScanThreads, tt = p / KMAX, ch = p % KMAX;
-            const bool ok = ch < K && tb + tt < t_hi;
-            rs[buf][tt][ch] = in_r[u];
-            ks[buf][tt][ch] = in_k[u];
-            if (MODE == 0) {
-                ds[buf][tt][ch] = ok ? expf(-expf(in_x[u] + w0c[u])) : 0.f;
-            } else {
-                ds[buf][tt][ch] = ok ? expf(-0.6065306597126334f * sigmoidf(in_x[u] + w0c[u])) : 0.f;
-                as[buf][tt][ch] = ok ? sigmoidf(in_y[u] + a0c[u]) : 0.f;
-            }
-        }
-        vs[buf][tid / kCols][tid % kCols] = in_v;
-    };
-    ask(t_lo);
-    put(0, t_lo);
-    __syncthreads();
+    fetch(0, t_lo);
     int buf = 0;
     for (int tb = t_lo; tb < t_hi; tb += kScanTokens, buf ^= 1) {
         const int n = min(kScanTokens, t_hi - tb);
-        const bool more = tb + kScanTokens < t_hi;
-        if (more) ask(tb + kScanTokens);
+        if (tb + kScanTokens < t_hi) {
+            fetch(buf ^ 1, tb + kScanTokens);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                                                  // the group of tokens has landed for every thread
 #pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
             const float vj = vs[buf][tt][jl];
-            const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][i0]);
-            const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][i0]);
-            const float4* d4 = reinterpret_cast<const float4*>(&ds[buf][tt][i0]);
+            const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][0]) + q;
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][0]) + q;
+            const float4* d4 = reinterpret_cast<const float4*>(&ds[buf][tt][0]) + q;
             float acc0 = 0.f, acc1 = 0.f;
             if (MODE == 0) {
-                const float4* u4 = reinterpret_cast<const float4*>(&us[i0]);
+                const float4* u4 = reinterpret_cast<const float4*>(&us[0]) + q;
 #pragma unroll
                 for (int c4 = 0; c4 < RPT / 4; ++c4) {
-                    const float4 rr = r4[c4], kk = k4[c4], dd = d4[c4], uu = u4[c4];
+                    const float4 rr = r4[c4 * kSplit], kk = k4[c4 * kSplit], dd = d4[c4 * kSplit], uu = u4[c4 * kSplit];
                     const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, kv4[4] = {kk.x, kk.y, kk.z, kk.w};
                     const float dv[4] = {dd.x, dd.y, dd.z, dd.w}, uv[4] = {uu.x, uu.y, uu.z, uu.w};
 #pragma unroll
@@ -135,11 +151,11 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
                     }
                 }
             } else {
-                const float4* a4 = reinterpret_cast<const float4*>(&as[buf][tt][i0]);
+                const float4* a4 = reinterpret_cast<const float4*>(&as[buf][tt][0]) + q;
                 float held = 0.f, kk2 = 0.f;               // this thread's share of k^T S (its column) and of |k|^2
 #pragma unroll
                 for (int c4 = 0; c4 < RPT / 4; ++c4) {
-                    const float4 kk = k4[c4];
+                    const float4 kk = k4[c4 * kSplit];
                     const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -156,7 +172,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
                 const float share = held / (kk2 + 1e-6f);
 #pragma unroll
                 for (int c4 = 0; c4 < RPT / 4; ++c4) {
-                    const float4 rr = r4[c4], kk = k4[c4], dd = d4[c4], aa = a4[c4];
+                    const float4 rr = r4[c4 * kSplit], kk = k4[c4 * kSplit], dd = d4[c4 * kSplit], aa = a4[c4 * kSplit];
                     const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, kv4[4] = {kk.x, kk.y, kk.z, kk.w};
                     const float dv[4] = {dd.x, dd.y, dd.z, dd.w}, av[4] = {aa.x, aa.y, aa.z, aa.w};
 #pragma unroll
@@ -173,13 +189,12 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput 
             for (int o = 1; o < kSplit; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && q == 0) out[(size_t)(tb + tt) * N * K + col] = acc;
         }
-        if (more) put(buf ^ 1, tb + kScanTokens);
-        __syncthreads();
+        __syncthreads();                                                  // before the next copies overwrite this half
     }
     if (live) {
 #pragma unroll
         for (int ii = 0; ii < RPT; ++ii)
-            if (i0 + ii < K) S_g[(size_t)(i0 + ii) * K + j] = S[ii];
+            if (row_of(ii) < K) S_g[(size_t)row_of(ii) * K + j] = S[ii];
     }
     if (MODE == 0 && last_in != nullptr && t_hi > t_lo) {
         float* prev = state + (size_t)slots[s] * state_stride + prev_off;
@@ -243,13 +258,13 @@ __global__ void tanh_rows_kernel(ScanInput in, TA* __restrict__ out, int T, int 
 }
 
 template <int MODE, typename TA>
-cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput x, ScanInput y,
-                        const float* w0, const float* a0, const float* bonus, float* state, long long stride, const int32_t* q_start,
-                        const int32_t* slots, float* out, const TA* last_in, int W, long long prev_off, int N, int K) {
-#define FORGE_SCAN_CASE(KM)                                                                                              \
-    case KM:                                                                                                             \
-        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, x, y, w0, a0, bonus, \
-                             state, stride, q_start, slots, out, last_in, W, prev_off, N, K);
+cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a,
+                        const float* bonus, float* state, long long stride, const int32_t* q_start, const int32_t* slots, float* out,
+                        const TA* last_in, int W, long long prev_off, int N, int K, int vec) {
+#define FORGE_SCAN_CASE(KM)                                                                                                  \
+    case KM:                                                                                                                 \
+        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, state, \
+                             stride, q_start, slots, out, last_in, W, prev_off, N, K, vec);
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
         default: return cudaErrorInvalidValue;
@@ -260,15 +275,16 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
 }  // namespace
 
 // mode 0 (decay and bonus) / 1 (generalized delta rule).  r, k, v, x (and y, mode 1): fp32, row t at p + t * ld, head n's
-// channels at columns n*K .. n*K+K-1.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  state: fp32 rows of state_stride
+// channels at columns n*K .. n*K+K-1; x (and y) are OVERWRITTEN with the decays (and removal rates) made from them; T: rows
+// of these matrices.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  state: fp32 rows of state_stride
 // numbers, row slots[s] holds request s's N matrices [K, K] from its start.  out fp32 [T, N*K].  last_in (mode 0, optional):
 // the mixer's input [T, W] of type last_dtype, whose last row per request is kept at state + prev_off.
 extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float* k, int ld_k, const float* v, int ld_v,
                                 const float* x, int ld_x, const float* y, int ld_y, const float* w0, const float* a0,
                                 const float* bonus, float* state, long long state_stride, const int32_t* q_start,
                                 const int32_t* slots, float* out, const void* last_in, int last_dtype, int W, long long prev_off,
-                                int S, int N, int K, cudaStream_t stream) {
-    if (S < 0 || N <= 0 || K <= 0 || (mode != 0 && mode != 1))
+                                int T, int S, int N, int K, cudaStream_t stream) {
+    if (T < 0 || S < 0 || N <= 0 || K <= 0 || (mode != 0 && mode != 1))
         return forge::fail(FORGE_ERR_ARG, "state_scan: bad sizes S=%d N=%d K=%d mode=%d", S, N, K, mode);
     if (K > 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "state_scan: heads of %d channels (at most 128)", K);
     if (state_stride < (long long)N * K * K) return forge::fail(FORGE_ERR_ARG, "state_scan: state rows are too short");
@@ -277,17 +293,27 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
     if (S == 0) return FORGE_OK;
     const int kmax = (K + 31) / 32 * 32;
     const dim3 grid(S, N, (K + kCols - 1) / kCols);
+    // decays (and removal rates) for all tokens at once, in place
+    {
+        const size_t n = (size_t)T * N * K;
+        const unsigned blocks = (unsigned)((n + 255) / 256);
+        cudaError_t g = mode == 0
+            ? forge::launch(scan_gates_kernel<0>, dim3(blocks), dim3(256), 0, stream, 1, const_cast<float*>(x), ld_x, (float*)nullptr, 0, w0, a0, T, N * K)
+            : forge::launch(scan_gates_kernel<1>, dim3(blocks), dim3(256), 0, stream, 1, const_cast<float*>(x), ld_x, const_cast<float*>(y), ld_y, w0, a0, T, N * K);
+        if (g != cudaSuccess) return forge::check_launch("state_scan (gates)", g);
+    }
     ScanInput R{r, ld_r}, Kk{k, ld_k}, V{v, ld_v}, X{x, ld_x}, Y{y, ld_y};
+    auto aligned = [](const float* p, int ld) { return p == nullptr || (((uintptr_t)p & 15) == 0 && ld % 4 == 0); };
+    const int vec = (K % 4 == 0 && aligned(r, ld_r) && aligned(k, ld_k) && aligned(x, ld_x) && aligned(y, ld_y)) ? 1 : 0;
     cudaError_t e;
     if (mode == 1) {
-        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, w0, a0, nullptr, state, state_stride, q_start, slots, out,
-                                  nullptr, 0, 0, N, K);
+        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, nullptr, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, vec);
     } else if (last_in == nullptr || last_dtype == FORGE_F32) {
-        e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, w0, nullptr, bonus, state, state_stride, q_start, slots, out,
-                                  (const float*)last_in, W, prev_off, N, K);
+        e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, bonus, state, state_stride, q_start, slots, out,
+                                  (const float*)last_in, W, prev_off, N, K, vec);
     } else {
-        e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, w0, nullptr, bonus, state, state_stride, q_start, slots,
-                                          out, (const __nv_bfloat16*)last_in, W, prev_off, N, K);
+        e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, bonus, state, state_stride, q_start, slots, out,
+                                          (const __nv_bfloat16*)last_in, W, prev_off, N, K, vec);
     }
     return forge::check_launch("state_scan", e);
 }

@@ -63,7 +63,7 @@ _SIGNATURES = {
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
         "forge_headmix_mma_supports": [_I, _I, _I, _I, _I],
         "forge_headmix_attention_mma": [_P] * 11 + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
-        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _P],
+        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
@@ -790,7 +790,8 @@ STATE_SCANS = {"decay_bonus": 0, "delta": 1}
 def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=None, last_in=None, prev_off=0):
     """The recurrence of a mixer with a [K, K] state per head (``kind``: "decay_bonus" or "delta", see csrc/recurrent.cu)
     over the step's tokens, request by request, from and into ``state`` fp32 [slots, row].  r, k, v, x, y: (fp32 matrix,
-    first column) pairs with N*K columns from there; returns fp32 [T, N*K].  ``last_in`` ("decay_bonus"): the mixer's input
+    first column) pairs with N*K columns from there; x (and y) are overwritten with the decays (and removal rates) made from
+    them; returns fp32 [T, N*K].  ``last_in`` ("decay_bonus"): the mixer's input
     [T, W], whose last row per request is kept in the state row at ``prev_off``."""
     lib = library("mixers")
     T = r[0].shape[0]
@@ -802,8 +803,9 @@ def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=
         STATE_SCANS[kind], rp, rl, kp, kl, vp, vl, xp, xl, yp, yl, _need(w0, "w0", torch.float32), _opt(a0, "a0", torch.float32),
         _opt(bonus, "bonus", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
         _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(out, "out", torch.float32),
-        _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), batch.num_requests, N, K,
+        _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), T, batch.num_requests, N, K,
         _stream()), "state_scan")
+    count_launches(1)              # the kernel that makes the decays (and removal rates) from x (and y), in place
     return out
 
 
