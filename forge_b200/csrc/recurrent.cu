@@ -31,24 +31,36 @@ constexpr int kSplit = 8;             // threads that share a column of S (each 
 constexpr int kCols = 16;             // columns of S per CTA
 constexpr int kScanThreads = kSplit * kCols;
 
-// What the recurrence multiplies with, made in place from what the projections gave, for all tokens at once:
-//   MODE 0: x <- exp(-exp(x + w0));   MODE 1: x <- exp(-exp(-1/2) sigmoid(x + w0)),  y <- sigmoid(y + a0)
+// What the recurrence multiplies with, made in place from what the projections gave, for all tokens at once, a warp per
+// (token, head):   MODE 0: x <- exp(-exp(x + w0));
+//                  MODE 1: x <- exp(-exp(-1/2) sigmoid(x + w0)),  y <- sigmoid(y + a0),  inv[t, head] = 1 / (|k|^2 + 1e-6)
 template <int MODE>
-__global__ void scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld_y, const float* __restrict__ w0,
-                                  const float* __restrict__ a0, int T, int NK) {
+__global__ void __launch_bounds__(128)
+scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld_y, const float* __restrict__ k, int ld_k,
+                  float* __restrict__ inv, const float* __restrict__ w0, const float* __restrict__ a0, int T, int N, int K) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)T * NK) return;
-    const size_t t = i / NK;
-    const int c = (int)(i % NK);
-    float* px = x + t * ld_x + c;
-    if (MODE == 0) {
-        *px = expf(-expf(*px + w0[c]));
-    } else {
-        *px = expf(-0.6065306597126334f * sigmoidf(*px + w0[c]));
-        float* py = y + t * ld_y + c;
-        *py = sigmoidf(*py + a0[c]);
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= T * N) return;
+    const size_t t = w / N;
+    const int head = w % N;
+    float kk = 0.f;
+    for (int ch = lane; ch < K; ch += 32) {
+        const int c = head * K + ch;
+        float* px = x + t * ld_x + c;
+        if (MODE == 0) {
+            *px = expf(-expf(*px + w0[c]));
+        } else {
+            *px = expf(-0.6065306597126334f * sigmoidf(*px + w0[c]));
+            float* py = y + t * ld_y + c;
+            *py = sigmoidf(*py + a0[c]);
+            const float kv = k[t * ld_k + c];
+            kk = fmaf(kv, kv, kk);
+        }
+    }
+    if (MODE == 1) {
+        kk = forge::warp_sum(kk);
+        if (lane == 0) inv[w] = 1.0f / (kk + 1e-6f);
     }
 }
 
@@ -71,12 +83,13 @@ __device__ __forceinline__ void stage_async(float* dst, const float* src, int by
 template <int KMAX, int MODE, typename TA>
 __global__ void __launch_bounds__(kScanThreads)
 state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a, const float* __restrict__ bonus,
-                  float* __restrict__ state, long long state_stride, const int32_t* __restrict__ q_start,
+                  const float* __restrict__ inv, float* __restrict__ state, long long state_stride, const int32_t* __restrict__ q_start,
                   const int32_t* __restrict__ slots, float* __restrict__ out, const TA* __restrict__ last_in, int W,
                   long long prev_off, int N, int K, int vec) {
     constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
     __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
     __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
+    __shared__ float is[2][kScanTokens];                                // MODE 1: 1 / (|k|^2 + 1e-6) of the staged tokens
     forge::pdl_launch_dependents();
     const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, jl = tid / kSplit, q = tid % kSplit;
     const int j = blockIdx.z * kCols + jl;
@@ -114,6 +127,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
         }
         const int tt = tid / kCols, jc = blockIdx.z * kCols + tid % kCols;              // values: this CTA's columns only
         if (tt < n && jc < K) stage_async(&vs[buf][tt][tid % kCols], v.p + (size_t)(tb + tt) * v.ld + head * K + jc, 4);
+        if (MODE == 1 && tid < n) stage_async(&is[buf][tid], inv + (size_t)(tb + tid) * N + head, 4);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     fetch(0, t_lo);
@@ -127,7 +141,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();                                                  // the group of tokens has landed for every thread
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < n; ++tt) {
             const float vj = vs[buf][tt][jl];
             const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][0]) + q;
@@ -152,24 +166,20 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
                 }
             } else {
                 const float4* a4 = reinterpret_cast<const float4*>(&as[buf][tt][0]) + q;
-                float held = 0.f, kk2 = 0.f;               // this thread's share of k^T S (its column) and of |k|^2
+                float held0 = 0.f, held1 = 0.f;            // this thread's share of k^T S (its column)
 #pragma unroll
                 for (int c4 = 0; c4 < RPT / 4; ++c4) {
                     const float4 kk = k4[c4 * kSplit];
-                    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        held = fmaf(kv4[e], S[c4 * 4 + e], held);
-                        kk2 = fmaf(kv4[e], kv4[e], kk2);
-                    }
+                    held0 = fmaf(kk.x, S[c4 * 4], held0);
+                    held1 = fmaf(kk.y, S[c4 * 4 + 1], held1);
+                    held0 = fmaf(kk.z, S[c4 * 4 + 2], held0);
+                    held1 = fmaf(kk.w, S[c4 * 4 + 3], held1);
                 }
+                float held = held0 + held1;
 #pragma unroll
-                for (int o = 1; o < kSplit; o <<= 1) {
-                    held += __shfl_xor_sync(0xffffffffu, held, o);
-                    kk2 += __shfl_xor_sync(0xffffffffu, kk2, o);
-                }
+                for (int o = 1; o < kSplit; o <<= 1) held += __shfl_xor_sync(0xffffffffu, held, o);
                 // (a * n)(n^T S) = a_i k_i (k^T S) / (|k|^2 + 1e-6): the two roots of the unit key multiply out
-                const float share = held / (kk2 + 1e-6f);
+                const float share = held * is[buf][tt];
 #pragma unroll
                 for (int c4 = 0; c4 < RPT / 4; ++c4) {
                     const float4 rr = r4[c4 * kSplit], kk = k4[c4 * kSplit], dd = d4[c4 * kSplit], aa = a4[c4 * kSplit];
@@ -259,11 +269,11 @@ __global__ void tanh_rows_kernel(ScanInput in, TA* __restrict__ out, int T, int 
 
 template <int MODE, typename TA>
 cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a,
-                        const float* bonus, float* state, long long stride, const int32_t* q_start, const int32_t* slots, float* out,
-                        const TA* last_in, int W, long long prev_off, int N, int K, int vec) {
+                        const float* bonus, const float* inv, float* state, long long stride, const int32_t* q_start, const int32_t* slots,
+                        float* out, const TA* last_in, int W, long long prev_off, int N, int K, int vec) {
 #define FORGE_SCAN_CASE(KM)                                                                                                  \
     case KM:                                                                                                                 \
-        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, state, \
+        return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, inv, state, \
                              stride, q_start, slots, out, last_in, W, prev_off, N, K, vec);
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
@@ -276,12 +286,12 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
 
 // mode 0 (decay and bonus) / 1 (generalized delta rule).  r, k, v, x (and y, mode 1): fp32, row t at p + t * ld, head n's
 // channels at columns n*K .. n*K+K-1; x (and y) are OVERWRITTEN with the decays (and removal rates) made from them; T: rows
-// of these matrices.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  state: fp32 rows of state_stride
+// of these matrices.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  inv (mode 1): fp32 [T, N] scratch for 1 / (|k|^2 + 1e-6).  state: fp32 rows of state_stride
 // numbers, row slots[s] holds request s's N matrices [K, K] from its start.  out fp32 [T, N*K].  last_in (mode 0, optional):
 // the mixer's input [T, W] of type last_dtype, whose last row per request is kept at state + prev_off.
 extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float* k, int ld_k, const float* v, int ld_v,
                                 const float* x, int ld_x, const float* y, int ld_y, const float* w0, const float* a0,
-                                const float* bonus, float* state, long long state_stride, const int32_t* q_start,
+                                const float* bonus, float* inv, float* state, long long state_stride, const int32_t* q_start,
                                 const int32_t* slots, float* out, const void* last_in, int last_dtype, int W, long long prev_off,
                                 int T, int S, int N, int K, cudaStream_t stream) {
     if (T < 0 || S < 0 || N <= 0 || K <= 0 || (mode != 0 && mode != 1))
@@ -293,13 +303,15 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
     if (S == 0) return FORGE_OK;
     const int kmax = (K + 31) / 32 * 32;
     const dim3 grid(S, N, (K + kCols - 1) / kCols);
-    // decays (and removal rates) for all tokens at once, in place
+    // decays (and removal rates, and the unit keys' divisors) for all tokens at once, in place
     {
-        const size_t n = (size_t)T * N * K;
-        const unsigned blocks = (unsigned)((n + 255) / 256);
+        if (mode == 1 && !inv) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs room for the keys' divisors");
+        const unsigned blocks = (unsigned)(((size_t)T * N + 3) / 4);
         cudaError_t g = mode == 0
-            ? forge::launch(scan_gates_kernel<0>, dim3(blocks), dim3(256), 0, stream, 1, const_cast<float*>(x), ld_x, (float*)nullptr, 0, w0, a0, T, N * K)
-            : forge::launch(scan_gates_kernel<1>, dim3(blocks), dim3(256), 0, stream, 1, const_cast<float*>(x), ld_x, const_cast<float*>(y), ld_y, w0, a0, T, N * K);
+            ? forge::launch(scan_gates_kernel<0>, dim3(blocks), dim3(128), 0, stream, 1, const_cast<float*>(x), ld_x, (float*)nullptr, 0,
+                            (const float*)nullptr, 0, (float*)nullptr, w0, a0, T, N, K)
+            : forge::launch(scan_gates_kernel<1>, dim3(blocks), dim3(128), 0, stream, 1, const_cast<float*>(x), ld_x, const_cast<float*>(y), ld_y,
+                            k, ld_k, inv, w0, a0, T, N, K);
         if (g != cudaSuccess) return forge::check_launch("state_scan (gates)", g);
     }
     ScanInput R{r, ld_r}, Kk{k, ld_k}, V{v, ld_v}, X{x, ld_x}, Y{y, ld_y};
@@ -307,12 +319,12 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
     const int vec = (K % 4 == 0 && aligned(r, ld_r) && aligned(k, ld_k) && aligned(x, ld_x) && aligned(y, ld_y)) ? 1 : 0;
     cudaError_t e;
     if (mode == 1) {
-        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, nullptr, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, vec);
+        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, nullptr, inv, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, vec);
     } else if (last_in == nullptr || last_dtype == FORGE_F32) {
-        e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, bonus, state, state_stride, q_start, slots, out,
+        e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, bonus, nullptr, state, state_stride, q_start, slots, out,
                                   (const float*)last_in, W, prev_off, N, K, vec);
     } else {
-        e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, bonus, state, state_stride, q_start, slots, out,
+        e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, bonus, nullptr, state, state_stride, q_start, slots, out,
                                           (const __nv_bfloat16*)last_in, W, prev_off, N, K, vec);
     }
     return forge::check_launch("state_scan", e);

@@ -63,7 +63,7 @@ _SIGNATURES = {
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
         "forge_headmix_mma_supports": [_I, _I, _I, _I, _I],
         "forge_headmix_attention_mma": [_P] * 11 + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
-        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _P],
+        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
@@ -799,9 +799,10 @@ def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=
     (rp, rl), (kp, kl), (vp, vl), (xp, xl) = _cols(*r), _cols(*k), _cols(*v), _cols(*x)
     yp, yl = _cols(*y) if y is not None else (None, 0)
     W = last_in.shape[1] if last_in is not None else 0
+    inv = new_tensor((T, N), torch.float32, r[0].device) if kind == "delta" else None       # the unit keys' divisors
     _check(lib, lib.forge_state_scan(
         STATE_SCANS[kind], rp, rl, kp, kl, vp, vl, xp, xl, yp, yl, _need(w0, "w0", torch.float32), _opt(a0, "a0", torch.float32),
-        _opt(bonus, "bonus", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
+        _opt(bonus, "bonus", torch.float32), _opt(inv, "inv", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
         _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(out, "out", torch.float32),
         _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), T, batch.num_requests, N, K,
         _stream()), "state_scan")

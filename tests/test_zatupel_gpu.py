@@ -77,6 +77,9 @@ ATTENTIONS = {
                       head_mix=False, head_gate=False),
     "one_kv_head_no_rotation": dict(num_heads=3, num_kv_heads=1, head_dim=8, v_head_dim=40, scale=0.5, window=30, keep_first=0, rot=0,
                                     theta=10.0, head_gate=False),
+    # more kept first tokens than a key tile holds, and a window far behind them: 150 tokens in other portions
+    "many_kept": dict(num_heads=4, num_kv_heads=2, head_dim=16, v_head_dim=8, scale=0.4, window=11, keep_first=70, rot=16, theta=50.0,
+                      tokens=150, cuts=[(0, 64), (64, 130), (130, 131), (131, 133), (133, 150)]),
     "blend": dict(num_heads=2, num_kv_heads=2, head_dim=32, v_head_dim=16, scale=0.2, window=7, keep_first=7, rot=32, theta=77.0,
                   head_mix=False, value_mix="blend"),
 }
@@ -89,18 +92,18 @@ def test_attention_mixer_alone(dtype, kind):
     from forge_b200.config import PartSpec
     from forge_b200.parts import build_part
     o = dict(ATTENTIONS[kind])
-    W, T = 40, 62
+    W, T, cuts = 40, o.pop("tokens", 62), o.pop("cuts", CUTS)
     rot, theta = o.pop("rot"), o.pop("theta")
     spec = PartSpec("headmix_attention", dict(o, hidden_size=W, position=PartSpec("rope_pairs", {"head_dim": o["head_dim"], "rotary_dims": rot,
                                                                                               "theta": theta})))
     mixer = build_part("mixer", spec, _rt(dtype))
     t, w = _bf16_weights(mixer, 0.35, seed=len(kind))
     mixer.bind(t)
-    storage = CacheStorage([mixer.cache_spec()], [None], 8, 24, 2, dtype, torch.device(DEV))
+    storage = CacheStorage([mixer.cache_spec()], [None], 8, 48, 2, dtype, torch.device(DEV))
     x = rand(T, W, seed=50).to(dtype)
     G, E = o["num_kv_heads"], o["v_head_dim"]
     v_first = rand(T, G * E, seed=51) if o.get("value_mix") == "blend" else None
-    got = _feed(mixer, storage, x, CUTS, requests=("a", "b"), shared=None if v_first is None else {"first_values": v_first})
+    got = _feed(mixer, storage, x, cuts, requests=("a", "b"), shared=None if v_first is None else {"first_values": v_first})
     m = {"heads": o["num_heads"], "kv_heads": G, "dim": o["head_dim"], "vdim": E, "scale": mixer.scale,
          "mask": {"size": o["window"] or 10 ** 6, "keep_first": o["keep_first"]}, "rot": {"base": theta, "dims": rot}}
     w.setdefault("talk", torch.eye(o["num_heads"], dtype=torch.float64))
