@@ -1,5 +1,6 @@
-"""forge_b200: a single-GPU inference engine for the dense LLaMA decoder on NVIDIA B200 (sm_100a),
-from a model folder (config.json + safetensors, or seeded random weights) to generated tokens.
+"""forge_b200: a single-GPU inference engine for the dense LLaMA decoder, and for the Zatupel hybrid of windowed
+attention and state-keeping mixers, on NVIDIA B200 (sm_100a), from a model folder (config.json + safetensors, or seeded
+random weights) to generated tokens.
 
     import forge_b200 as forge
     model = forge.Model(model_dir, device="cuda", dtype="bfloat16")

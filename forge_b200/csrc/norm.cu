@@ -89,7 +89,54 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* _
     for (int c = threadIdx.x; c < H; c += kNormThreads) o[c] = forge::from_float<TOut>(xr[c] * inv * w[c]);
 }
 
+// Two norms of the same rows with the same eps and different weights (the two branches of a parallel block): one read
+// of the residual stream, one reduction, two outputs.
+template <typename TOut>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ w2, TOut* __restrict__ out1,
+                    TOut* __restrict__ out2, int H, float eps) {
+    __shared__ float red[32];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const float* xr = x + (size_t)blockIdx.x * H;
+    TOut* o1 = out1 + (size_t)blockIdx.x * H;
+    TOut* o2 = out2 + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    if ((H & 3) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        for (int c = threadIdx.x; c < (H >> 2); c += kNormThreads) {
+            const float4 v = x4[c];
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+        ss = forge::block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int c = threadIdx.x; c < (H >> 2); c += kNormThreads) {
+            const float4 v = x4[c], g = reinterpret_cast<const float4*>(w1)[c], h = reinterpret_cast<const float4*>(w2)[c];
+            Pack4<TOut>::store(o1 + 4 * c, v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+            Pack4<TOut>::store(o2 + 4 * c, v.x * inv * h.x, v.y * inv * h.y, v.z * inv * h.z, v.w * inv * h.w);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < H; c += kNormThreads) ss = fmaf(xr[c], xr[c], ss);
+    ss = forge::block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += kNormThreads) {
+        o1[c] = forge::from_float<TOut>(xr[c] * inv * w1[c]);
+        o2[c] = forge::from_float<TOut>(xr[c] * inv * w2[c]);
+    }
+}
+
 }  // namespace
+
+extern "C" int forge_rmsnorm_pair(const float* x, const float* w1, const float* w2, void* out1, void* out2, int out_dtype, int R, int H,
+                                  float eps, cudaStream_t stream) {
+    if (R < 0 || H <= 0) return forge::fail(FORGE_ERR_ARG, "rmsnorm_pair: bad sizes R=%d H=%d", R, H);
+    if (R == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(out_dtype, TO,
+        e = forge::launch(rmsnorm_pair_kernel<TO>, dim3(R), dim3(kNormThreads), 0, stream, 1, x, w1, w2, (TO*)out1, (TO*)out2, H, eps));
+    return forge::check_launch("rmsnorm_pair", e);
+}
 
 extern "C" int forge_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int32_t* rows,
                              int R, int H, float eps, cudaStream_t stream) {

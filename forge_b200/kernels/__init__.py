@@ -34,6 +34,7 @@ _SIGNATURES = {
     "core": {
         "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "forge_rmsnorm_pair": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
         "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "forge_rope_table": [_P, _P, _I, _I, _F, _I, _P],
         "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _I, _P],
@@ -526,6 +527,19 @@ def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
                                   _need(out, "out", out_dtype), dtype_code(out_dtype),
                                   _opt(rows, "rows", torch.int32), R, H, float(eps), _stream()), "rmsnorm")
     return out
+
+
+def rmsnorm_pair(x, w1, w2, eps, out_dtype):
+    """(x * rsqrt(mean(x^2)+eps) * w1, the same * w2) over the rows of float32 x [T,H]: one read, one reduction."""
+    lib = library("core")
+    T, H = x.shape
+    if w1.numel() != H or w2.numel() != H:
+        raise KernelError(f"rmsnorm_pair: weights of {w1.numel()} and {w2.numel()} elements, rows have {H}")
+    o1, o2 = new_tensor((T, H), out_dtype, x.device), new_tensor((T, H), out_dtype, x.device)
+    _check(lib, lib.forge_rmsnorm_pair(_need(x, "x", torch.float32, 2), _need(w1, "w1", torch.float32), _need(w2, "w2", torch.float32),
+                                       _need(o1, "out1", out_dtype), _need(o2, "out2", out_dtype), dtype_code(out_dtype), T, H,
+                                       float(eps), _stream()), "rmsnorm_pair")
+    return o1, o2
 
 
 def rope_table(positions, head_dim, theta, by_pair=False):

@@ -109,9 +109,18 @@ class ParallelBlock(Part):
         for part in self._children():
             part.bind({name: tensors[name] for name in part.tensor_specs() if name in tensors})
 
+    def _norms(self, residual):
+        from .. import kernels
+        from .norm import RMSNorm
+        a, b = self.norm_mixer, self.norm_ff
+        if b is None:
+            return a.forward(residual), None
+        if type(a) is RMSNorm and type(b) is RMSNorm and a.eps == b.eps and a.size == b.size:
+            return kernels.rmsnorm_pair(residual, a.weight, b.weight, a.eps, self.rt.dtype)      # one read of the residual
+        return a.forward(residual), b.forward(residual)
+
     def forward(self, residual, batch, cache):
-        x = self.norm_mixer.forward(residual)
-        x_ff = None if self.norm_ff is None else self.norm_ff.forward(residual)
+        x, x_ff = self._norms(residual)
         self.mixer.forward(x, batch, cache, residual)
         if x_ff is not None:
             self.feed_forward.forward(x_ff, residual)
