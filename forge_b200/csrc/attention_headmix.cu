@@ -40,7 +40,8 @@ headmix_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __
     TC* kbase = cache + (size_t)page * page_stride;
     TC* vbase = kbase + (size_t)G * page_size * D;
     const int n_qk = (H + G) * D;
-    for (int idx = threadIdx.x; idx < n_qk; idx += blockDim.x) {
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;      // a row's work is spread over the CTAs of its grid row
+    for (int idx = first; idx < n_qk; idx += step) {
         const int head = idx / D, d = idx % D;
         float x = row[idx];
         if (d < rot_dims) {
@@ -54,14 +55,14 @@ headmix_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __
     }
     const int n_v = G * E;
     const float l = (v_first && lam) ? lam[0] : 0.f;
-    for (int idx = threadIdx.x; idx < n_v; idx += blockDim.x) {
+    for (int idx = first; idx < n_v; idx += step) {
         float x = row[n_qk + idx];
         if (v_keep) v_keep[(size_t)t * n_v + idx] = x;
         if (v_first) x = (1.0f - l) * x + l * v_first[(size_t)t * n_v + idx];
         if (store) vbase[((size_t)(idx / E) * page_size + off) * E + idx % E] = forge::from_float<TC>(x);
     }
     if (has_gate)
-        for (int h = threadIdx.x; h < H; h += blockDim.x)
+        for (int h = first; h < H; h += step)
             gate_out[(size_t)t * H + h] = 1.0f / (1.0f + expf(-row[n_qk + n_v + h]));
 }
 
@@ -233,7 +234,7 @@ extern "C" int forge_headmix_prepare(const float* proj, int ld, const int32_t* p
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(headmix_prepare_kernel<TT>, dim3(T), dim3(128), 0, stream, 1, proj, ld, positions, slot_mapping, inv_freq,
+        e = forge::launch(headmix_prepare_kernel<TT>, dim3(T, T >= 256 ? 1 : ((H + G) * D + 511) / 512), dim3(128), 0, stream, 1, proj, ld, positions, slot_mapping, inv_freq,
                           v_first, lam, v_keep, (TT*)q_out, (TT*)cache, gate_out, H, G, D, E, rot_dims, page_size, page_stride, has_gate));
     return forge::check_launch("headmix_prepare", e);
 }

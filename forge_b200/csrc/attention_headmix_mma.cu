@@ -60,12 +60,12 @@ template <int VC>
 __global__ void __launch_bounds__(kThreads)
 headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                    const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
-                   const int32_t* __restrict__ tile_n, float* __restrict__ u, int H, int G, int D, int E, int page_size,
-                   long long page_stride, int max_pages, int window, int keep_first, float scale) {
+                   const int32_t* __restrict__ tile_n, float* __restrict__ u, float* __restrict__ part_ml, int nsplit, int T, int H,
+                   int G, int D, int E, int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
-    const int tile = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * VC;
+    const int tile = blockIdx.x / nsplit, sp = blockIdx.x % nsplit, c = blockIdx.y, v0 = blockIdx.z * VC;
     const int t0 = tile_t0 ? tile_t0[tile] : tile;
     const int nq = tile_n ? tile_n[tile] : 1;
     if (!FORGE_TOKEN_OK(t0) || !FORGE_TOKEN_OK(t0 + nq - 1)) return;
@@ -142,11 +142,14 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
         copies_commit();
     };
-    fetch(0, 0);
-    for (int ti = 0; ti < n_tiles; ++ti) {
+    // nsplit > 1 (steps of single tokens): the key tiles are dealt out to nsplit CTAs in runs; each leaves its sums as they
+    // are, with the row's maximum and sum, and the second kernel puts the runs together
+    const int per = (n_tiles + nsplit - 1) / nsplit, ti_lo = sp * per, ti_hi = min(n_tiles, ti_lo + per);
+    if (ti_lo < ti_hi) fetch(ti_lo, ti_lo & 1);
+    for (int ti = ti_lo; ti < ti_hi; ++ti) {
         const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
         const int j0 = kt * BN;
-        if (ti + 1 < n_tiles) {
+        if (ti + 1 < ti_hi) {
             fetch(ti + 1, (ti + 1) & 1);
             copies_wait<1>();
         } else {
@@ -244,13 +247,18 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
         __syncthreads();                                                  // before the next fetch writes into this buffer's twin's successor
     }
-    // normalise and store this chunk's columns of u
-    const float inv[2] = {row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f, row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f};
+    // normalise and store this chunk's columns of u (one run of tiles: final; several: as they are, beside maximum and sum)
+    const float inv[2] = {nsplit > 1 ? 1.0f : (row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f), nsplit > 1 ? 1.0f : (row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f)};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = h ? r_hi : r_lo;
         if (r >= rows) continue;
-        float* dst = u + ((size_t)(t0 + r / Gq) * H + c * Gq + r % Gq) * GE;
+        const size_t row_index = (size_t)(t0 + r / Gq) * H + c * Gq + r % Gq;
+        float* dst = u + ((size_t)sp * T * H + row_index) * GE;
+        if (nsplit > 1 && blockIdx.z == 0 && (lane & 3) == 0) {
+            part_ml[((size_t)sp * T * H + row_index) * 2] = row_m[h];
+            part_ml[((size_t)sp * T * H + row_index) * 2 + 1] = row_l[h];
+        }
 #pragma unroll
         for (int nt = 0; nt < VC / 8; ++nt) {
             const int col = v0 + nt * 8 + (lane & 3) * 2;
@@ -263,8 +271,8 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // One CTA per (token, key/value head c): the H x E block of u that the query heads of c read goes to shared memory
 // once (rows of E consecutive numbers), then a thread per (head of c, channel) takes its sum over g.
 __global__ void __launch_bounds__(128)
-headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ mix, const float* __restrict__ gate,
-                       __nv_bfloat16* __restrict__ out, int H, int G, int E) {
+headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, int T, const float* __restrict__ mix,
+                       const float* __restrict__ gate, __nv_bfloat16* __restrict__ out, int H, int G, int E) {
     extern __shared__ float sm[];
     forge::pdl_launch_dependents();
     const int t = blockIdx.x, c = blockIdx.y, GE = G * E, Gq = H / G;
@@ -273,8 +281,25 @@ headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ mi
     if (mix) for (int i = threadIdx.x; i < Gq * H; i += blockDim.x) mx[i] = mix[(size_t)c * Gq * H + i];
     forge::pdl_wait();
     const float* ut = u + (size_t)t * H * GE + (size_t)c * E;
+    // u of head g: as the first kernel left it, or put together from the runs of key tiles: sum_s 2^(m_s - m) u_s / sum_s 2^(m_s - m) l_s
+    auto u_of = [&](int g, int e) {
+        if (nsplit <= 1) return ut[(size_t)g * GE + e];
+        float m = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, part_ml[((size_t)sp * T * H + (size_t)t * H + g) * 2]);
+        float num = 0.f, den = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const size_t row = (size_t)sp * T * H + (size_t)t * H + g;
+            const float l = part_ml[row * 2 + 1];
+            if (l > 0.f) {                                   // a run that saw no key left nothing to read
+                const float w = exp2f(part_ml[row * 2] - m);
+                num = fmaf(w, u[row * GE + (size_t)c * E + e], num);
+                den = fmaf(w, l, den);
+            }
+        }
+        return den > 0.f ? num / den : 0.f;
+    };
     if (mix) {
-        for (int i = threadIdx.x; i < H * E; i += blockDim.x) ub[i] = ut[(size_t)(i / E) * GE + i % E];
+        for (int i = threadIdx.x; i < H * E; i += blockDim.x) ub[i] = u_of(i / E, i % E);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < Gq * E; i += blockDim.x) {
@@ -292,7 +317,7 @@ headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ mi
             for (; g < H; ++g) a0 = fmaf(mx[hq * H + g], ub[g * E + e], a0);
             a = (a0 + a1) + (a2 + a3);
         } else {
-            a = ut[(size_t)h * GE + e];
+            a = u_of(h, e);
         }
         if (gate) a *= gate[(size_t)t * H + h];
         out[((size_t)t * H + h) * E + e] = __float2bfloat16_rn(a);
@@ -304,7 +329,8 @@ forge::PerDeviceFlag g_attr_done[3], g_combine_done;
 template <int VC>
 int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u,
-               int H, int G, int D, int E, int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale) {
+               float* part_ml, int nsplit, int T, int H, int G, int D, int E, int page_size, long long page_stride, int max_pages, int window,
+               int keep_first, float scale) {
     bool& done = g_attr_done[which].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -313,7 +339,7 @@ int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __n
     }
     return forge::check_launch("headmix_attention_mma",
                                forge::launch(headmix_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions,
-                                             t0, tn, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
+                                             t0, tn, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
 }
 
 }  // namespace
@@ -325,31 +351,34 @@ extern "C" int forge_headmix_mma_supports(int H, int G, int D, int E, int page_s
     return (page_size > 0 && (page_size & (page_size - 1)) == 0 && H > 0 && G > 0 && H % G == 0 && H / G <= BM && H <= 96 && D % 16 == 0 && D >= 16 && D <= 128 && E % 8 == 0 && E > 0) ? 1 : 0;
 }
 
-// q bf16 [T, H*D]; u fp32 [T, H, G*E] (scratch); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive tokens of one
+// q bf16 [T, H*D]; u fp32 [nsplit, T, H, G*E] (scratch); part_ml fp32 [nsplit, T, H, 2] (scratch, nsplit > 1: steps of single
+// tokens whose key tiles are dealt out to nsplit CTAs); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive tokens of one
 // request with tile_n * (H/G) <= 64 (both null: one token per tile, num_tiles = T).  mix fp32 [H, H] or null; gate fp32
 // [T, H] or null.
 extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                            const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* mix,
-                                           const float* gate, float* u, void* out, int T, int num_tiles, int H, int G, int D, int E,
+                                           const float* gate, float* u, float* part_ml, int nsplit, void* out, int T, int num_tiles, int H, int G, int D, int E,
                                            int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale,
                                            cudaStream_t stream) {
     if (!forge_headmix_mma_supports(H, G, D, E, page_size)) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_attention_mma: H=%d G=%d D=%d E=%d", H, G, D, E);
     if (T < 0 || num_tiles < 0 || page_size <= 0 || max_pages <= 0 || keep_first < 0 || (tile_t0 == nullptr) != (tile_n == nullptr))
         return forge::fail(FORGE_ERR_ARG, "headmix_attention_mma: bad arguments");
     if (T == 0 || num_tiles == 0) return FORGE_OK;
+    if (nsplit < 1 || nsplit > 16 || (nsplit > 1 && (tile_t0 != nullptr || part_ml == nullptr)))
+        return forge::fail(FORGE_ERR_ARG, "headmix_attention_mma: the keys are dealt out to several CTAs only in steps of single tokens");
     const int GE = G * E;
     int VC = 64;                        // the chunk width that wastes the fewest columns; among equals the widest
     for (int cand : {128, 256})
         if ((GE + cand - 1) / cand * cand <= (GE + VC - 1) / VC * VC) VC = cand;
     const int chunks = (GE + VC - 1) / VC;
     const size_t smem = sizeof(__nv_bfloat16) * ((size_t)(BM + 2 * BN) * (D + kPad) + 2 * (size_t)BN * (VC + kPad));
-    const dim3 grid(num_tiles, G, chunks);
+    const dim3 grid(num_tiles * nsplit, G, chunks);
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     int rc;
-    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     if (rc != FORGE_OK) return rc;
     const size_t csmem = mix ? sizeof(float) * ((size_t)(H / G) * H + (size_t)H * E) : 0;
     if (csmem > 160 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_combine: %d heads of %d channels", H, E);
@@ -360,7 +389,7 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
         cdone = true;
     }
     return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T, G), dim3(128), csmem, stream, 1,
-                                                                (const float*)u, mix, gate, (__nv_bfloat16*)out, H, G, E));
+                                                                (const float*)u, (const float*)part_ml, nsplit, T, mix, gate, (__nv_bfloat16*)out, H, G, E));
 }
 
 FORGE_DEFINE_CHECKS_ENTRY(attention_headmix_mma)

@@ -226,7 +226,9 @@ token_shift_kernel(const TA* __restrict__ h, const float* __restrict__ state, lo
     const int t = blockIdx.x, s = tok_req[t];
     const bool first = t == q_start[s];
     const float* kept = state + (size_t)slots[s] * state_stride + prev_off;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    // (a step of few tokens spreads a row over several CTAs: a thread's loads are a chain, and eight CTAs walking 2,048
+    // columns took 26 us)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         const float cur = forge::to_float(h[(size_t)t * W + c]);
         const float prev = first ? kept[c] : forge::to_float(h[(size_t)(t - 1) * W + c]);
         for (int m = 0; m < n_mix; ++m)
@@ -338,7 +340,7 @@ extern "C" int forge_token_shift(const void* h, const float* state, long long st
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(token_shift_kernel<TT>, dim3(T), dim3(128), 0, stream, 1, (const TT*)h, state, state_stride, prev_off, tok_req,
+        e = forge::launch(token_shift_kernel<TT>, dim3(T, T >= 256 ? 1 : (W + 511) / 512), dim3(128), 0, stream, 1, (const TT*)h, state, state_stride, prev_off, tok_req,
                           q_start, slots, mu, (TT*)out, T, W, n_mix));
     return forge::check_launch("token_shift", e);
 }

@@ -63,7 +63,7 @@ _SIGNATURES = {
         "forge_headmix_prepare": [_P, _I] + [_P] * 9 + [_I] * 8 + [_LL, _I, _P],
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
         "forge_headmix_mma_supports": [_I, _I, _I, _I, _I],
-        "forge_headmix_attention_mma": [_P] * 11 + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
+        "forge_headmix_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -766,13 +766,21 @@ def headmix_attention(q, cache, group_batch, batch, H, G, D, E, page_size, scale
     if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_headmix_mma_supports.fn(H, G, D, E, page_size):
         # tensor cores: one pass per head over all key/value heads' values, then the exchange between heads
         t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
-        u = new_tensor((T, H, G * E), torch.float32, q.device)
+        nsplit = 1
+        if getattr(batch, "decode_only", False):
+            # a step of single tokens brings T * G * (value chunks) CTAs: deal a request's key tiles out to several, up to
+            # one CTA per SM, as far as the longest context (the graph's bucket) and the window have tiles
+            ctas = T * G * -(-(G * E) // 256)
+            reach = min(batch.max_context, (window + (keep_first or 0)) if window else batch.max_context)
+            nsplit = max(1, min(8, -(-reach // 64), _sm_count(q.device) // max(1, ctas)))
+        u = new_tensor((nsplit, T, H, G * E), torch.float32, q.device)
+        part_ml = new_tensor((nsplit, T, H, 2), torch.float32, q.device) if nsplit > 1 else None
         out = new_tensor((T, H * E), q.dtype, q.device)
         _check(lib, lib.forge_headmix_attention_mma(
             _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
             _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
             _opt(tn, "tile_n", torch.int32), _opt(mix, "mix", torch.float32), _opt(gate, "gate", torch.float32), _need(u, "u", torch.float32),
-            _need(out, "out", torch.bfloat16), T, tiles, H, G, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
+            _opt(part_ml, "part_ml", torch.float32), nsplit, _need(out, "out", torch.bfloat16), T, tiles, H, G, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
             int(window or 0), int(keep_first or 0), float(scale), _stream()), "headmix_attention_mma")
         count_launches(1)          # the kernel that takes the sum over heads
         return out
