@@ -38,7 +38,10 @@ template <int MODE>
 __global__ void __launch_bounds__(128)
 scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld_y, const float* __restrict__ k, int ld_k,
                   float* __restrict__ inv, const float* __restrict__ w0, const float* __restrict__ a0, int T, int N, int K) {
-    forge::pdl_launch_dependents();
+    // No early word to the scheduler here: the kernel that follows is the scan, whose few CTAs each walk a request's tokens
+    // for the whole of its time.  Let in while this kernel's many blocks fill the SMs, they were placed wherever there was
+    // room, several on one SM and none on others, and the delta rule's scan took 850 us instead of 290 (1,024 tokens, 32
+    // heads of 64).  They are let in when this grid's blocks exit and the SMs are free.
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= T * N) return;
