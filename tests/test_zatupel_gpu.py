@@ -80,6 +80,10 @@ ATTENTIONS = {
     # more kept first tokens than a key tile holds, and a window far behind them: 150 tokens in other portions
     "many_kept": dict(num_heads=4, num_kv_heads=2, head_dim=16, v_head_dim=8, scale=0.4, window=11, keep_first=70, rot=16, theta=50.0,
                       tokens=150, cuts=[(0, 64), (64, 130), (130, 131), (131, 133), (133, 150)]),
+    # all key/value heads' values side by side make 128 and 256 columns: the tensor-core kernel's other two chunk widths
+    "values_128_wide": dict(num_heads=4, num_kv_heads=2, head_dim=16, v_head_dim=64, scale=0.35, window=25, keep_first=2, rot=8, theta=900.0),
+    "values_256_wide": dict(num_heads=4, num_kv_heads=4, head_dim=32, v_head_dim=64, scale=0.25, window=40, keep_first=0, rot=32, theta=1e4,
+                            head_gate=False),
     "blend": dict(num_heads=2, num_kv_heads=2, head_dim=32, v_head_dim=16, scale=0.2, window=7, keep_first=7, rot=32, theta=77.0,
                   head_mix=False, value_mix="blend"),
 }
@@ -174,7 +178,8 @@ def test_one_key_that_stands_out(dtype, page_size, D, E):
         storage.manager.check()
 
 
-STATE_MIXERS = [("wkv", 5, 16, 8), ("wkv", 1, 40, 24), ("wkv", 2, 64, 4), ("general_delta", 3, 24, 12), ("general_delta", 4, 8, 16),
+STATE_MIXERS = [("wkv", 3, 10, 4), ("general_delta", 2, 6, 4),          # channels that are no multiple of four: staged one by one
+                ("wkv", 5, 16, 8), ("wkv", 1, 40, 24), ("wkv", 2, 64, 4), ("general_delta", 3, 24, 12), ("general_delta", 4, 8, 16),
                 ("general_delta", 1, 96, 8), ("wkv", 2, 128, 8), ("general_delta", 2, 128, 8)]
 
 
