@@ -270,7 +270,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // out[t, h, e] = gate[t, h] * sum_g mix[h, g] u[t, g, kv(h) * E + e]      (mix null: u[t, h, ...] alone)
 // One CTA per (token, key/value head c): the H x E block of u that the query heads of c read goes to shared memory
 // once (rows of E consecutive numbers), then a thread per (head of c, channel) takes its sum over g.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, int T, const float* __restrict__ mix,
                        const float* __restrict__ gate, __nv_bfloat16* __restrict__ out, int H, int G, int E) {
     extern __shared__ float sm[];
@@ -281,24 +281,35 @@ headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ pa
     if (mix) for (int i = threadIdx.x; i < Gq * H; i += blockDim.x) mx[i] = mix[(size_t)c * Gq * H + i];
     forge::pdl_wait();
     const float* ut = u + (size_t)t * H * GE + (size_t)c * E;
-    // u of head g: as the first kernel left it, or put together from the runs of key tiles: sum_s 2^(m_s - m) u_s / sum_s 2^(m_s - m) l_s
-    auto u_of = [&](int g, int e) {
-        if (nsplit <= 1) return ut[(size_t)g * GE + e];
-        float m = -INFINITY;
-        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, part_ml[((size_t)sp * T * H + (size_t)t * H + g) * 2]);
-        float num = 0.f, den = 0.f;
-        for (int sp = 0; sp < nsplit; ++sp) {
-            const size_t row = (size_t)sp * T * H + (size_t)t * H + g;
-            const float l = part_ml[row * 2 + 1];
-            if (l > 0.f) {                                   // a run that saw no key left nothing to read
-                const float w = exp2f(part_ml[row * 2] - m);
-                num = fmaf(w, u[row * GE + (size_t)c * E + e], num);
+    // Several runs of key tiles (nsplit > 1): run s of head g counts with 2^(m_s - m) / sum_s 2^(m_s - m) l_s; a thread per
+    // head works the weights out once, then every value is nsplit independent loads.
+    float* wsp = ub + (mix || nsplit > 1 ? H * E : 0);     // [H][nsplit]
+    if (nsplit > 1) {
+        for (int g = threadIdx.x; g < H; g += blockDim.x) {
+            float m = -INFINITY, den = 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, part_ml[((size_t)sp * T * H + (size_t)t * H + g) * 2]);
+            for (int sp = 0; sp < nsplit; ++sp) {
+                const size_t row = (size_t)sp * T * H + (size_t)t * H + g;
+                const float l = part_ml[row * 2 + 1];
+                const float w = l > 0.f ? exp2f(part_ml[row * 2] - m) : 0.f;        // a run that saw no key counts for nothing
+                wsp[g * nsplit + sp] = w;
                 den = fmaf(w, l, den);
             }
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) wsp[g * nsplit + sp] *= inv;
         }
-        return den > 0.f ? num / den : 0.f;
+        __syncthreads();
+    }
+    auto u_of = [&](int g, int e) {
+        if (nsplit <= 1) return ut[(size_t)g * GE + e];
+        float a = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float w = wsp[g * nsplit + sp];
+            if (w > 0.f) a = fmaf(w, u[((size_t)sp * T * H + (size_t)t * H + g) * GE + (size_t)c * E + e], a);
+        }
+        return a;
     };
-    if (mix) {
+    if (mix || nsplit > 1) {
         for (int i = threadIdx.x; i < H * E; i += blockDim.x) ub[i] = u_of(i / E, i % E);
     }
     __syncthreads();
@@ -317,7 +328,7 @@ headmix_combine_kernel(const float* __restrict__ u, const float* __restrict__ pa
             for (; g < H; ++g) a0 = fmaf(mx[hq * H + g], ub[g * E + e], a0);
             a = (a0 + a1) + (a2 + a3);
         } else {
-            a = u_of(h, e);
+            a = nsplit > 1 ? ub[h * E + e] : ut[(size_t)h * GE + e];
         }
         if (gate) a *= gate[(size_t)t * H + h];
         out[((size_t)t * H + h) * E + e] = __float2bfloat16_rn(a);
@@ -380,7 +391,7 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     if (rc != FORGE_OK) return rc;
-    const size_t csmem = mix ? sizeof(float) * ((size_t)(H / G) * H + (size_t)H * E) : 0;
+    const size_t csmem = sizeof(float) * ((mix ? (size_t)(H / G) * H : 0) + (mix || nsplit > 1 ? (size_t)H * E : 0) + (nsplit > 1 ? (size_t)H * nsplit : 0));
     if (csmem > 160 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_combine: %d heads of %d channels", H, E);
     bool& cdone = g_combine_done.current();
     if (!cdone) {
@@ -388,7 +399,7 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
         if (e != cudaSuccess) return forge::check_launch("headmix_combine (shared memory)", e);
         cdone = true;
     }
-    return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T, G), dim3(128), csmem, stream, 1,
+    return forge::check_launch("headmix_combine", forge::launch(headmix_combine_kernel, dim3(T, G), dim3(256), csmem, stream, 1,
                                                                 (const float*)u, (const float*)part_ml, nsplit, T, mix, gate, (__nv_bfloat16*)out, H, G, E));
 }
 

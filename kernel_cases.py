@@ -94,7 +94,56 @@ def case(name):
     if name == "attention_prefill_mma":      # the same through the mma.sync kernel, for comparison
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
-    raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
+    if name in ("headmix_attention_prefill", "headmix_attention_decode"):
+        # attention whose heads exchange weights: 32 / 4 kv heads of 64, window 1,024 + 4 kept first tokens, pages of 64;
+        # one request of 2,048 tokens (12.9 GFLOP of Q K^T and P V for the visible pairs; the kernel executes 32.3: the value
+        # product runs over all 4 kv heads' values), or 8 requests of one token on 1,023 cached
+        from forge_b200.kernels import headmix_attention
+        ps, window, keep = 64, 1024, 4
+        reqs = [(0, 2048)] if name.endswith("prefill") else [(1023, 1)] * 8
+        pages_per = [-(-(c + n) // ps) for c, n in reqs]
+        table = torch.full((len(reqs), max(pages_per)), -1, dtype=torch.int32)
+        q_start, nxt = [0], 0
+        for s_, n in enumerate(pages_per):
+            table[s_, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+            nxt += n
+            q_start.append(q_start[-1] + reqs[s_][1])
+        T = q_start[-1]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(num_requests=len(reqs), num_tokens=T, host_q_start=q_start, attention_plan={},
+                                tok_req=i32([s_ for s_, (c, n) in enumerate(reqs) for _ in range(n)]),
+                                positions=i32([c + j for c, n in reqs for j in range(n)]))
+        if name.endswith("decode"):
+            batch.decode_only, batch.max_context = True, 1024
+        g = SimpleNamespace(block_table=table.to(DEV))
+        q, cache = _bf16(T, NH * HD), _bf16(nxt, 2, NKV, ps, HD)
+        mix, gate = torch.eye(NH, device=DEV) + 0.1 * torch.randn(NH, NH, device=DEV), torch.rand(T, NH, device=DEV)
+        pairs = sum(min(c + j + 1, window + keep) for c, n in reqs for j in range(n))
+        return (lambda: headmix_attention(q, cache, g, batch, NH, NKV, HD, HD, ps, HD ** -0.5, window=window, keep_first=keep, mix=mix,
+                                          gate=gate)), pairs * NKV * 2 * HD * 2 // max(1, T // len(reqs)), 2 * pairs * NH * 2 * HD
+    if name in ("state_scan_wkv", "state_scan_delta"):
+        # the recurrence of a state mixer alone: one request of 1,024 tokens, 32 heads of 64 channels (6 or 8 FLOPs per state
+        # element and token), with the kernel that makes the decays in front of it
+        from forge_b200.kernels import state_scan
+        T, N, K = 1024, 32, 64
+        mk = lambda: torch.randn(T, N * K, device=DEV) * 0.5
+        r, k, v, x, y = mk(), mk(), mk(), mk(), mk()
+        x0, y0 = x.clone(), y.clone()
+        w0, u = torch.randn(N * K, device=DEV), torch.randn(N * K, device=DEV)
+        state = torch.zeros(2, N * K * K, device=DEV)
+        i32 = lambda z: torch.tensor(z, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(q_start=i32([0, T]), slots=i32([1]), num_requests=1)
+
+        def run():
+            x.copy_(x0)             # the scan overwrites x (and y) with the decays (and removal rates)
+            y.copy_(y0)
+            if name.endswith("delta"):
+                state_scan("delta", (r, 0), (k, 0), (v, 0), (x, 0), w0, state, batch, N, K, y=(y, 0), a0=w0)
+            else:
+                state_scan("decay_bonus", (r, 0), (k, 0), (v, 0), (x, 0), w0, state, batch, N, K, bonus=u)
+        return run, 4 * T * N * K * 4, (8 if name.endswith("delta") else 6) * T * N * K * K
+    raise SystemExit(f"unknown case {name!r}; known: headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
+                     "gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "
                      "attention_prefill_hd128 attention_prefill_mma attention_prefill_shared_keys")
