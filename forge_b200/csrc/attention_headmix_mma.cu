@@ -20,6 +20,7 @@
 namespace {
 
 constexpr int BM = 64, BN = 64, kThreads = 128, kPad = 8;
+constexpr int kMmaSmemLimit = 200 * 1024;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -60,7 +61,7 @@ template <int VC>
 __global__ void __launch_bounds__(kThreads)
 headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                    const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
-                   const int32_t* __restrict__ tile_n, float* __restrict__ u, float* __restrict__ part_ml, int nsplit, int T, int H,
+                   const int32_t* __restrict__ tile_n, float* __restrict__ u, float* __restrict__ part_ml, int nsplit, int nstages, int T, int H,
                    int G, int D, int E, int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
@@ -75,8 +76,8 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int DP = D + kPad, VP = VC + kPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][D + 8]
     const int stage = BN * (DP + VP);                                     // elements of one buffer: a key tile and a value tile
-    __nv_bfloat16* Ks = Qs + BM * DP;                                     // 2 x [BN][D + 8]
-    __nv_bfloat16* Vs = Ks + BN * DP;                                     // 2 x [BN][VC + 8], each behind its key tile
+    __nv_bfloat16* Ks = Qs + BM * DP;                                     // nstages x [BN][D + 8]
+    __nv_bfloat16* Vs = Ks + BN * DP;                                     // nstages x [BN][VC + 8], each behind its key tile
     __shared__ int voff[VC / 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -95,7 +96,12 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
     for (int i = 0; i < VC / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
     float row_m[2] = {-INFINITY, -INFINITY}, row_l[2] = {0.f, 0.f};
-    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;           // this thread's two rows
+    // A tile of at most 16 rows (a single token: H/G rows) would leave three warps idle: there all four warps take the same
+    // 16 rows, each computes the scores again, and each takes a quarter of the value columns.
+    const bool colsplit = rows <= 16;
+    const int rb = colsplit ? 0 : warp;                                   // this warp's block of 16 rows
+    const int ntw = colsplit ? VC / 32 : VC / 8, cb = colsplit ? warp * (VC / 4) : 0;     // its value columns: ntw blocks of 8 from cb
+    const int r_lo = rb * 16 + (lane >> 2), r_hi = r_lo + 8;             // this thread's two rows
     const int pos_lo = pos0 + min(r_lo, rows - 1) / Gq, pos_hi = pos0 + min(r_hi, rows - 1) / Gq;
     const bool live_lo = r_lo < rows, live_hi = r_hi < rows;
 
@@ -145,107 +151,118 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     // nsplit > 1 (steps of single tokens): the key tiles are dealt out to nsplit CTAs in runs; each leaves its sums as they
     // are, with the row's maximum and sum, and the second kernel puts the runs together
     const int per = (n_tiles + nsplit - 1) / nsplit, ti_lo = sp * per, ti_hi = min(n_tiles, ti_lo + per);
-    if (ti_lo < ti_hi) fetch(ti_lo, ti_lo & 1);
+    // nstages buffers: tiles ti + 1 .. ti + nstages - 1 are on their way while tile ti is worked on (two for prompt portions,
+    // whose tiles are long work; more for single tokens, where a tile is little work and a copy's latency is what counts).
+    // A group of copies is committed per tile, an empty one past the end, so that "all but the newest nstages - 1" always
+    // means that tile ti has landed.
+    for (int p = 0; p < nstages - 1; ++p) {
+        if (ti_lo + p < ti_hi) fetch(ti_lo + p, p);
+        else copies_commit();
+    }
     for (int ti = ti_lo; ti < ti_hi; ++ti) {
         const int kt = ti < kept_tiles ? ti : first_win_tile + (ti - kept_tiles);
         const int j0 = kt * BN;
-        if (ti + 1 < ti_hi) {
-            fetch(ti + 1, (ti + 1) & 1);
-            copies_wait<1>();
-        } else {
-            copies_wait<0>();
-        }
+        const int ahead = ti + nstages - 1;
+        if (ahead < ti_hi) fetch(ahead, (ahead - ti_lo) % nstages);
+        else copies_commit();
+        if (nstages == 2) copies_wait<1>();
+        else if (nstages == 3) copies_wait<2>();
+        else copies_wait<3>();
         __syncthreads();                                                  // tile ti has landed for every thread
-        const __nv_bfloat16* Kt = Ks + (ti & 1) * stage;
-        const __nv_bfloat16* Vt = Vs + (ti & 1) * stage;
+        const __nv_bfloat16* Kt = Ks + ((ti - ti_lo) % nstages) * stage;
+        const __nv_bfloat16* Vt = Vs + ((ti - ti_lo) % nstages) * stage;
 
-        // S = Q K^T for this warp's 16 rows and the tile's 64 keys
-        float sacc[BN / 8][4];
-#pragma unroll
-        for (int i = 0; i < BN / 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
-        for (int k0 = 0; k0 < D; k0 += 16) {
-            uint32_t a[4];
-            ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * DP + k0 + (lane >> 4) * 8);
-#pragma unroll
-            for (int nt = 0; nt < BN / 8; nt += 2) {
-                uint32_t b[4];      // keys nt*8 .. nt*8+15: (b0, b1) of the first eight, (b0, b1) of the next eight
-                ldmatrix_x4(b, Kt + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * DP + k0 + ((lane >> 3) & 1) * 8);
-                mma_bf16(sacc[nt], a, b[0], b[1]);
-                mma_bf16(sacc[nt + 1], a, b[2], b[3]);
-            }
-        }
-        // scale, mask, and the tile's maximum per row.  A tile that every row of the CTA sees whole needs no mask.
-        const bool whole = rows == BM && j0 + BN - 1 <= pos0 && (window <= 0 || pos_last - j0 < window || j0 + BN - 1 < keep_first);
-        float tmax[2] = {-INFINITY, -INFINITY};
-        if (whole) {
-#pragma unroll
-            for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    sacc[nt][e] *= sl2;
-                    tmax[e >> 1] = fmaxf(tmax[e >> 1], sacc[nt][e]);
+        // a warp whose 16 rows lie beyond the tile's rows (a single token brings H/G rows) has nothing to compute
+        if (rb * 16 < rows) {
+            // S = Q K^T for this warp's 16 rows and the tile's 64 keys
+            float sacc[BN / 8][4];
+    #pragma unroll
+            for (int i = 0; i < BN / 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+            for (int k0 = 0; k0 < D; k0 += 16) {
+                uint32_t a[4];
+                ldmatrix_x4(a, Qs + (rb * 16 + (lane & 15)) * DP + k0 + (lane >> 4) * 8);
+    #pragma unroll
+                for (int nt = 0; nt < BN / 8; nt += 2) {
+                    uint32_t b[4];      // keys nt*8 .. nt*8+15: (b0, b1) of the first eight, (b0, b1) of the next eight
+                    ldmatrix_x4(b, Kt + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * DP + k0 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(sacc[nt], a, b[0], b[1]);
+                    mma_bf16(sacc[nt + 1], a, b[2], b[3]);
                 }
             }
-        } else {
-#pragma unroll
+            // scale, mask, and the tile's maximum per row.  A tile that every row of the CTA sees whole needs no mask.
+            const bool whole = rows == BM && j0 + BN - 1 <= pos0 && (window <= 0 || pos_last - j0 < window || j0 + BN - 1 < keep_first);
+            float tmax[2] = {-INFINITY, -INFINITY};
+            if (whole) {
+    #pragma unroll
+                for (int nt = 0; nt < BN / 8; ++nt) {
+    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        sacc[nt][e] *= sl2;
+                        tmax[e >> 1] = fmaxf(tmax[e >> 1], sacc[nt][e]);
+                    }
+                }
+            } else {
+    #pragma unroll
+                for (int nt = 0; nt < BN / 8; ++nt) {
+    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const bool hi = e >= 2;
+                        const bool ok = (hi ? live_hi : live_lo) && visible(hi ? pos_hi : pos_lo, j, window, keep_first);
+                        const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
+                        sacc[nt][e] = s;
+                        tmax[hi] = fmaxf(tmax[hi], s);
+                    }
+                }
+            }
+            float alpha[2], base[2];
+    #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+                tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+                const float m_new = fmaxf(row_m[h], tmax[h]);
+                base[h] = m_new == -INFINITY ? 0.f : m_new;                   // a row that has seen nothing yet
+                alpha[h] = ex2(row_m[h] - base[h]);                         // exp2(-inf) = 0
+                row_m[h] = m_new;
+            }
+            float tsum[2] = {0.f, 0.f};
+            uint32_t pa[BN / 16][4];                                          // P as the A operand, 16 keys per k-step
+    #pragma unroll
             for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const bool hi = e >= 2;
-                    const bool ok = (hi ? live_hi : live_lo) && visible(hi ? pos_hi : pos_lo, j, window, keep_first);
-                    const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
-                    sacc[nt][e] = s;
-                    tmax[hi] = fmaxf(tmax[hi], s);
+                const float p0 = ex2(sacc[nt][0] - base[0]), p1 = ex2(sacc[nt][1] - base[0]);
+                const float p2 = ex2(sacc[nt][2] - base[1]), p3 = ex2(sacc[nt][3] - base[1]);
+                tsum[0] += p0 + p1;
+                tsum[1] += p2 + p3;
+                pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+                pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+    #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 1);
+                tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 2);
+                row_l[h] = row_l[h] * alpha[h] + tsum[h];
+            }
+    #pragma unroll
+            for (int i = 0; i < VC / 8; ++i) {
+                oacc[i][0] *= alpha[0];
+                oacc[i][1] *= alpha[0];
+                oacc[i][2] *= alpha[1];
+                oacc[i][3] *= alpha[1];
+            }
+            // O += P V
+    #pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+    #pragma unroll
+                for (int nt = 0; nt < VC / 8; nt += 2) {
+                    if (nt >= ntw) break;                                 // (the same for the whole warp)
+                    uint32_t b[4];      // keys kk*16 .. +15 (rows), columns cb + nt*8 .. +15: matrices (k lo, n lo), (k hi, n lo), (k lo, n hi), (k hi, n hi)
+                    ldmatrix_x4_trans(b, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + cb + nt * 8 + (lane >> 4) * 8);
+                    mma_bf16(oacc[nt], pa[kk], b[0], b[1]);
+                    mma_bf16(oacc[nt + 1], pa[kk], b[2], b[3]);
                 }
             }
         }
-        float alpha[2], base[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
-            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
-            const float m_new = fmaxf(row_m[h], tmax[h]);
-            base[h] = m_new == -INFINITY ? 0.f : m_new;                   // a row that has seen nothing yet
-            alpha[h] = ex2(row_m[h] - base[h]);                         // exp2(-inf) = 0
-            row_m[h] = m_new;
-        }
-        float tsum[2] = {0.f, 0.f};
-        uint32_t pa[BN / 16][4];                                          // P as the A operand, 16 keys per k-step
-#pragma unroll
-        for (int nt = 0; nt < BN / 8; ++nt) {
-            const float p0 = ex2(sacc[nt][0] - base[0]), p1 = ex2(sacc[nt][1] - base[0]);
-            const float p2 = ex2(sacc[nt][2] - base[1]), p3 = ex2(sacc[nt][3] - base[1]);
-            tsum[0] += p0 + p1;
-            tsum[1] += p2 + p3;
-            pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
-            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 1);
-            tsum[h] += __shfl_xor_sync(0xffffffffu, tsum[h], 2);
-            row_l[h] = row_l[h] * alpha[h] + tsum[h];
-        }
-#pragma unroll
-        for (int i = 0; i < VC / 8; ++i) {
-            oacc[i][0] *= alpha[0];
-            oacc[i][1] *= alpha[0];
-            oacc[i][2] *= alpha[1];
-            oacc[i][3] *= alpha[1];
-        }
-        // O += P V
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-#pragma unroll
-            for (int nt = 0; nt < VC / 8; nt += 2) {
-                uint32_t b[4];      // keys kk*16 .. +15 (rows), columns nt*8 .. +15: matrices (k lo, n lo), (k hi, n lo), (k lo, n hi), (k hi, n hi)
-                ldmatrix_x4_trans(b, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nt * 8 + (lane >> 4) * 8);
-                mma_bf16(oacc[nt], pa[kk], b[0], b[1]);
-                mma_bf16(oacc[nt + 1], pa[kk], b[2], b[3]);
-            }
-        }
-        __syncthreads();                                                  // before the next fetch writes into this buffer's twin's successor
+        __syncthreads();                                                  // before a later fetch writes into this buffer
     }
     // normalise and store this chunk's columns of u (one run of tiles: final; several: as they are, beside maximum and sum)
     const float inv[2] = {nsplit > 1 ? 1.0f : (row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f), nsplit > 1 ? 1.0f : (row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f)};
@@ -255,13 +272,14 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         if (r >= rows) continue;
         const size_t row_index = (size_t)(t0 + r / Gq) * H + c * Gq + r % Gq;
         float* dst = u + ((size_t)sp * T * H + row_index) * GE;
-        if (nsplit > 1 && blockIdx.z == 0 && (lane & 3) == 0) {
+        if (nsplit > 1 && blockIdx.z == 0 && (lane & 3) == 0 && (!colsplit || warp == 0)) {
             part_ml[((size_t)sp * T * H + row_index) * 2] = row_m[h];
             part_ml[((size_t)sp * T * H + row_index) * 2 + 1] = row_l[h];
         }
 #pragma unroll
         for (int nt = 0; nt < VC / 8; ++nt) {
-            const int col = v0 + nt * 8 + (lane & 3) * 2;
+            if (nt >= ntw) break;
+            const int col = v0 + cb + nt * 8 + (lane & 3) * 2;
             if (col < GE) *reinterpret_cast<float2*>(dst + col) = make_float2(oacc[nt][2 * h] * inv[h], oacc[nt][2 * h + 1] * inv[h]);
         }
     }
@@ -340,17 +358,17 @@ forge::PerDeviceFlag g_attr_done[3], g_combine_done;
 template <int VC>
 int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u,
-               float* part_ml, int nsplit, int T, int H, int G, int D, int E, int page_size, long long page_stride, int max_pages, int window,
-               int keep_first, float scale) {
+               float* part_ml, int nsplit, int nstages, int T, int H, int G, int D, int E, int page_size, long long page_stride, int max_pages,
+               int window, int keep_first, float scale) {
     bool& done = g_attr_done[which].current();
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
         if (e != cudaSuccess) return forge::check_launch("headmix_attention_mma (shared memory)", e);
         done = true;
     }
     return forge::check_launch("headmix_attention_mma",
                                forge::launch(headmix_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions,
-                                             t0, tn, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
+                                             t0, tn, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
 }
 
 }  // namespace
@@ -382,14 +400,19 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     for (int cand : {128, 256})
         if ((GE + cand - 1) / cand * cand <= (GE + VC - 1) / VC * VC) VC = cand;
     const int chunks = (GE + VC - 1) / VC;
-    const size_t smem = sizeof(__nv_bfloat16) * ((size_t)(BM + 2 * BN) * (D + kPad) + 2 * (size_t)BN * (VC + kPad));
+    // buffers for key/value tiles: two.  (Three and four for steps of single tokens measured no faster at 8 requests and
+    // slower at 64, where they cost the second CTA of an SM: such a step's time is the live warps' tensor work, not the copies.)
+    const size_t q_bytes = sizeof(__nv_bfloat16) * (size_t)BM * (D + kPad);
+    const size_t stage_bytes = sizeof(__nv_bfloat16) * (size_t)BN * ((D + kPad) + (VC + kPad));
+    const int nstages = 2;
+    const size_t smem = q_bytes + nstages * stage_bytes;
     const dim3 grid(num_tiles * nsplit, G, chunks);
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     int rc;
-    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     if (rc != FORGE_OK) return rc;
     const size_t csmem = sizeof(float) * ((mix ? (size_t)(H / G) * H : 0) + (mix || nsplit > 1 ? (size_t)H * E : 0) + (nsplit > 1 ? (size_t)H * nsplit : 0));
     if (csmem > 160 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_combine: %d heads of %d channels", H, E);
