@@ -61,7 +61,7 @@ template <int VC>
 __global__ void __launch_bounds__(kThreads)
 headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                    const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
-                   const int32_t* __restrict__ tile_n, float* __restrict__ u, float* __restrict__ part_ml, int nsplit, int nstages, int T, int H,
+                   const int32_t* __restrict__ tile_n, float* __restrict__ u, float* __restrict__ part_ml, int nsplit, int nstages, int qrows, int T, int H,
                    int G, int D, int E, int page_size, long long page_stride, int max_pages, int window, int keep_first, float scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
@@ -76,7 +76,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int DP = D + kPad, VP = VC + kPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][D + 8]
     const int stage = BN * (DP + VP);                                     // elements of one buffer: a key tile and a value tile
-    __nv_bfloat16* Ks = Qs + BM * DP;                                     // nstages x [BN][D + 8]
+    __nv_bfloat16* Ks = Qs + qrows * DP;                                  // nstages x [BN][D + 8]   (qrows: 64, or 16 for single tokens)
     __nv_bfloat16* Vs = Ks + BN * DP;                                     // nstages x [BN][VC + 8], each behind its key tile
     __shared__ int voff[VC / 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -84,7 +84,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
     // queries: row r = token t0 + r / Gq, head c * Gq + r % Gq
     const int dchunks = D >> 3;
-    for (int i = tid; i < BM * dchunks; i += kThreads) {
+    for (int i = tid; i < qrows * dchunks; i += kThreads) {
         const int r = i / dchunks, ch = i % dchunks;
         uint4 val = zero4;
         if (r < rows)
@@ -244,6 +244,7 @@ headmix_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             }
     #pragma unroll
             for (int i = 0; i < VC / 8; ++i) {
+                if (i >= ntw) break;
                 oacc[i][0] *= alpha[0];
                 oacc[i][1] *= alpha[0];
                 oacc[i][2] *= alpha[1];
@@ -358,8 +359,8 @@ forge::PerDeviceFlag g_attr_done[3], g_combine_done;
 template <int VC>
 int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u,
-               float* part_ml, int nsplit, int nstages, int T, int H, int G, int D, int E, int page_size, long long page_stride, int max_pages,
-               int window, int keep_first, float scale) {
+               float* part_ml, int nsplit, int nstages, int qrows, int T, int H, int G, int D, int E, int page_size, long long page_stride,
+               int max_pages, int window, int keep_first, float scale) {
     bool& done = g_attr_done[which].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
@@ -368,7 +369,7 @@ int launch_mma(int which, dim3 grid, size_t smem, cudaStream_t stream, const __n
     }
     return forge::check_launch("headmix_attention_mma",
                                forge::launch(headmix_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions,
-                                             t0, tn, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
+                                             t0, tn, u, part_ml, nsplit, nstages, qrows, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale));
 }
 
 }  // namespace
@@ -402,7 +403,9 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     const int chunks = (GE + VC - 1) / VC;
     // buffers for key/value tiles: two.  (Three and four for steps of single tokens measured no faster at 8 requests and
     // slower at 64, where they cost the second CTA of an SM: such a step's time is the live warps' tensor work, not the copies.)
-    const size_t q_bytes = sizeof(__nv_bfloat16) * (size_t)BM * (D + kPad);
+    // a step of single tokens brings H/G rows a tile: 16 rows of queries in shared memory leave room for a second CTA on the SM
+    const int qrows = (tile_t0 == nullptr && H / G <= 16) ? 16 : BM;
+    const size_t q_bytes = sizeof(__nv_bfloat16) * (size_t)qrows * (D + kPad);
     const size_t stage_bytes = sizeof(__nv_bfloat16) * (size_t)BN * ((D + kPad) + (VC + kPad));
     const int nstages = 2;
     const size_t smem = q_bytes + nstages * stage_bytes;
@@ -410,9 +413,9 @@ extern "C" int forge_headmix_attention_mma(const void* q, const void* cache, con
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     int rc;
-    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
-    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    if (VC == 64) rc = launch_mma<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, qrows, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else if (VC == 128) rc = launch_mma<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, qrows, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
+    else rc = launch_mma<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, part_ml, nsplit, nstages, qrows, T, H, G, D, E, page_size, page_stride, max_pages, window, keep_first, scale);
     if (rc != FORGE_OK) return rc;
     const size_t csmem = sizeof(float) * ((mix ? (size_t)(H / G) * H : 0) + (mix || nsplit > 1 ? (size_t)H * E : 0) + (nsplit > 1 ? (size_t)H * nsplit : 0));
     if (csmem > 160 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "headmix_combine: %d heads of %d channels", H, E);
