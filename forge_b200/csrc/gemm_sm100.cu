@@ -18,7 +18,8 @@
 //   1  C fp32 += acc + bias                      (the residual stream)
 //   2  C bf16  = acc + bias
 //   3  C bf16[M, N/2]: out[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]     (gate/up rows interleaved in W)
-//   5  the same with gelu_tanh(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) as the gate's activation
+//   5  the same with gelu_tanh(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) as the gate's activation (a build with
+//      -DFORGE_GATE_GELU=1 only)
 // Replaces the reference's cuBLAS GemmEx / tiled GEMM / GEMV trio and its separate bias-add, residual-add
 // and silu-multiply launches (src/operators/cuda/cuda_quant.cu:582-599, cuda_gemm.cu:7-55,
 // cuda_elementwise.cu:8-48).
@@ -60,11 +61,22 @@ template <int BN> struct Cfg {
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers*/ + 2 * kOutBytes;
 };
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
-__device__ __forceinline__ float gelu_tanh(float g) { return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))); }
-// the gate's activation of the two gated epilogues
+// The gate's activation of the gated epilogues.  Both are g * sigmoid(y): silu with y = g, and the tanh form of gelu,
+// g/2 (1 + tanh z) with z = sqrt(2/pi) (g + 0.044715 g^3), because (1 + tanh z) / 2 = sigmoid(2 z).  The polynomial and the
+// select cost the silu epilogues 0.3 to 2 % of a LLaMA step (measured), so only a library built with -DFORGE_GATE_GELU=1
+// has them (and takes epilogue 5); the ordinary build's gated epilogue is silu alone, as it was.
+#ifndef FORGE_GATE_GELU
+#define FORGE_GATE_GELU 0
+#endif
 __device__ __forceinline__ bool is_gated(int epilogue) { return epilogue == EPI_SWIGLU_BF16 || epilogue == EPI_GEGLU_BF16; }
-__device__ __forceinline__ float gate_act(int epilogue, float g) { return epilogue == EPI_GEGLU_BF16 ? gelu_tanh(g) : silu(g); }
+__device__ __forceinline__ float gate_act(int epilogue, float g) {
+#if FORGE_GATE_GELU
+    const float y = epilogue == EPI_GEGLU_BF16 ? 1.5957691216057308f * fmaf(0.044715f * g * g, g, g) : g;
+    return g / (1.0f + __expf(-y));
+#else
+    return g / (1.0f + __expf(-g));
+#endif
+}
 
 // Applies the epilogue to 32 consecutive columns (n .. n+31) of output row m held in r (fp32 bits) and stores them.
 template <int BN>
@@ -1747,6 +1759,8 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     if (M == 0) return FORGE_OK;
     if (K % 8 != 0) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: K=%d is not a multiple of 8 (TMA row stride)", K);
     if (epilogue < 0 || epilogue == EPI_QKV_ROPE || epilogue > EPI_GEGLU_BF16) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: unknown epilogue %d", epilogue);
+    if (epilogue == EPI_GEGLU_BF16 && !FORGE_GATE_GELU)
+        return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: the gelu gate is in the library built with -DFORGE_GATE_GELU=1");
     if ((epilogue == EPI_SWIGLU_BF16 || epilogue == EPI_GEGLU_BF16) && (N & 1)) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: a gated epilogue needs even N, got %d", N);
     if (g_num_sms == 0) {
         int dev = 0;

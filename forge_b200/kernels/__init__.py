@@ -1229,13 +1229,15 @@ def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_d
 
 
 EPILOGUES = {"none": 0, "accumulate": 1, "cast": 2, "swiglu": 3, "geglu": 5}
+GELU_GATE_VARIANT = {"FORGE_GATE_GELU": 1}
 
 
 def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None):
     """bf16 x [M,K] . w [N,K]^T on the tcgen05 tensor cores, fp32 accumulation.
     epilogue "none": fp32 [M,N] (added into ``accumulate_into`` when given); "cast": bf16 [M,N];
     "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]; "geglu": the same with the tanh form of gelu."""
-    lib = library("gemm_sm100")
+    # the gelu gate lives in a variant of the library of its own, so that the silu epilogues stay as short as they were
+    lib = library("gemm_sm100", GELU_GATE_VARIANT) if epilogue == "geglu" else library("gemm_sm100")
     (M, K), (N, K2) = x.shape, w.shape
     if K != K2:
         raise KernelError(f"gemm_sm100: x {tuple(x.shape)} does not match w {tuple(w.shape)}")
@@ -1300,7 +1302,7 @@ GEMM_WORKSPACE_BYTES = 48 * 1024 * 1024
 
 def _gemm_workspace(lib, device):
     """One zeroed buffer per device for the few-rows GEMM's partial sums and flags, given to the library once."""
-    key = str(device)
+    key = (id(lib), str(device))           # a variant of the library is a library of its own, with a workspace of its own
     if key not in _workspaces:
         ws = torch.zeros(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
         with torch.cuda.device(device), once_per_step():

@@ -147,4 +147,5 @@ def build_all(force=False):
                 out[f"{name}_hd{hd}"] = build_library(name, force=force, defines={"FORGE_ATT_HD": hd})
         else:
             out[name] = build_library(name, force=force)
+    out["gemm_sm100_gate_gelu1"] = build_library("gemm_sm100", force=force, defines={"FORGE_GATE_GELU": 1})
     return out
