@@ -30,3 +30,19 @@ def test_reference_arm_without_a_build_says_why(tmp_path):
     assert rc == 0 and len(lines) == 1
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and "not built" in d["unavailable"] and "\n" not in d["unavailable"]
+
+
+def test_the_design_option_keeps_to_one_gpu_and_counts_its_shapes():
+    rc, lines = _run("--design", "zatupel", "--gpus", "2")
+    assert rc == 2 and len(lines) == 1 and "single-GPU" in json.loads(lines[0])["error"]
+    # the shapes it measures are configurations that load, and their matrices are counted from the configuration alone
+    sys.path.insert(0, ROOT)
+    import bench
+    from forge_b200.config import config_from_dict
+    z = dict(width=256, layers=4, heads=8, kv_heads=2, dim=32, ff=512, state_heads=4, state_dim=32, rank=16, window=64, vocab=300)
+    cfg = config_from_dict(bench.zatupel_shape(**z))
+    assert [l["type"] for l in cfg.layers] == ["attention", "wkv", "attention", "general_delta"]
+    layers, head = bench.zatupel_matmul_params(cfg)
+    att = 256 * (8 * 32 + 2 * 32 + 2 * 32 + 8) + 256 * 8 * 32
+    state = lambda n: 256 * 128 * n + 16 * (256 + 128)
+    assert layers == 2 * att + state(5) + state(6) + 4 * 3 * 256 * 512 and head == 300 * 256
