@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from ..parts.base import KVCacheSpec, StateSpec
+from ..parts.base import CompositeCacheSpec, KVCacheSpec, StateSpec
 from .manager import CacheManager, GroupSpec
 from .pages import CacheError
 
@@ -26,6 +26,7 @@ class LayerCache:
     kv: Optional[torch.Tensor] = None          # [num_pages, 2, NKV, page_size, HD]; value heads of another size: [num_pages, row]
     state: Optional[torch.Tensor] = None       # [max_requests, *shape]
     writable: bool = True
+    parts: Optional[list] = None               # a mixer made of mixers: one LayerCache per inner mixer
 
 
 def group_name(spec: KVCacheSpec):
@@ -34,12 +35,28 @@ def group_name(spec: KVCacheSpec):
     return f"kv{spec.num_kv_heads}x{spec.head_dim}{v}_{w}"
 
 
+def kv_specs_of(spec):
+    """The key/value specs inside a spec (a composite one may hold several, at any depth)."""
+    if isinstance(spec, KVCacheSpec):
+        return [spec]
+    if isinstance(spec, CompositeCacheSpec):
+        return [s for p in spec.parts for s in kv_specs_of(p)]
+    return []
+
+
 def plan_groups(cache_specs, cache_from):
-    """cache_specs: per layer KVCacheSpec | StateSpec | None.  Returns ({group name: KVCacheSpec},
-    per-layer group name or None)."""
+    """cache_specs: per layer KVCacheSpec | StateSpec | CompositeCacheSpec | None.  Returns ({group name: KVCacheSpec},
+    per-layer group name or None; a composite layer's inner caches name their groups themselves)."""
     groups, layer_group = {}, []
     for i, spec in enumerate(cache_specs):
         src = cache_from[i]
+        if isinstance(spec, CompositeCacheSpec):
+            if src is not None:
+                raise CacheError(f"layer {i}: a mixer made of several cannot read another layer's cache")
+            for s in kv_specs_of(spec):
+                groups[group_name(s)] = s
+            layer_group.append(None)
+            continue
         if src is not None:
             s2 = cache_specs[src]
             if cache_from[src] is not None:
@@ -63,8 +80,9 @@ def bytes_per_page(cache_specs, cache_from, page_size, dtype):
     el = torch.empty((), dtype=dtype).element_size()
     out = {g: 0 for g in groups}
     for i, spec in enumerate(cache_specs):
-        if cache_from[i] is None and isinstance(spec, KVCacheSpec):
-            out[layer_group[i]] += spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim) * el
+        if cache_from[i] is None:
+            for s in kv_specs_of(spec):
+                out[group_name(s)] += s.num_kv_heads * page_size * (s.head_dim + s.value_dim) * el
     return out
 
 
@@ -84,23 +102,30 @@ class CacheStorage:
             if cache_from[i] is not None:
                 self.layers.append(None)       # filled below
                 continue
-            if isinstance(spec, KVCacheSpec):
-                shape = (2, spec.num_kv_heads, page_size, spec.head_dim) if spec.value_dim == spec.head_dim else \
-                    (spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim),)
-                kv = self._guarded_zeros(f"keys/values of run {i}", (pages_per_group[self.layer_group[i]], *shape), dtype)
-                self.layers.append(LayerCache(self.layer_group[i], page_size, kv=kv))
-            elif isinstance(spec, StateSpec):
-                st = self._guarded_zeros(f"state of run {i}", (max_requests, *spec.shape), spec.dtype)
-                self._state_tensors.append(st)
-                self.layers.append(LayerCache(None, page_size, state=st))
-            elif spec is None:
-                self.layers.append(LayerCache(None, page_size))
-            else:
-                raise CacheError(f"layer {i}: unknown cache spec {spec!r}")
+            self.layers.append(self._make(spec, f"run {i}", pages_per_group))
         for i, src in enumerate(cache_from):
             if src is not None:
                 s = self.layers[src]
                 self.layers[i] = LayerCache(s.group, page_size, kv=s.kv, state=s.state, writable=False)
+
+    def _make(self, spec, what, pages_per_group):
+        page_size = self.page_size
+        if isinstance(spec, KVCacheSpec):
+            shape = (2, spec.num_kv_heads, page_size, spec.head_dim) if spec.value_dim == spec.head_dim else \
+                (spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim),)
+            name = group_name(spec)
+            kv = self._guarded_zeros(f"keys/values of {what}", (pages_per_group[name], *shape), self.dtype)
+            return LayerCache(name, page_size, kv=kv)
+        if isinstance(spec, StateSpec):
+            st = self._guarded_zeros(f"state of {what}", (self.max_requests, *spec.shape), spec.dtype)
+            self._state_tensors.append(st)
+            return LayerCache(None, page_size, state=st)
+        if isinstance(spec, CompositeCacheSpec):
+            return LayerCache(None, page_size, parts=[self._make(s, f"{what}, mixer {k}", pages_per_group)
+                                                      for k, s in enumerate(spec.parts)])
+        if spec is None:
+            return LayerCache(None, page_size)
+        raise CacheError(f"{what}: unknown cache spec {spec!r}")
 
     # Canary words: every cache tensor is allocated with one more page (or state row) in front and one behind, filled
     # with a fixed bit pattern that nothing ever writes.  A kernel that follows a page id of -1 or num_pages (or a slot

@@ -1,6 +1,7 @@
 from .base import ConfigError, LayerSpec, ModelPlan, PartSpec
 from .llama import LlamaConfig
 from .zatupel import ZatupelConfig
+from .tidenex import TidenexConfig
 from .registry import (config_from_dict, load_config, register_architecture, registered_architectures,
                        unregister_architecture)
 
@@ -12,5 +13,8 @@ register_architecture("Qwen2ForCausalLM", LlamaConfig, replace=True)
 # a hybrid of windowed attention and two state-keeping mixers; its files name it with one string, "architecture"
 register_architecture("Zatupel", ZatupelConfig, replace=True)
 
-__all__ = ["ZatupelConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
+# pre-norm layers of differential attention, or of an attention beside a gated linear recurrence; a span of layers may repeat
+register_architecture("Tidenex", TidenexConfig, replace=True)
+
+__all__ = ["ZatupelConfig", "TidenexConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture"]

@@ -22,7 +22,8 @@ class LayerSpec:
     """One layer: how its parts are arranged (``block``), the parts, and where its tensors live.
 
     ``cache_from``: index (into ``ModelPlan.layers``) of another layer whose cache this layer's mixer
-    reads instead of keeping one of its own.
+    reads instead of keeping one of its own.  ``norm_prefixes``: what the names of each norm's tensors start with
+    (None: the block arrangement's own).
     """
     block: str
     mixer: PartSpec
@@ -30,6 +31,7 @@ class LayerSpec:
     norms: Dict[str, PartSpec]
     weight_prefix: str
     cache_from: Optional[int] = None
+    norm_prefixes: Optional[Dict[str, str]] = None
 
 
 @dataclass(frozen=True)
@@ -46,6 +48,8 @@ class ModelPlan:
     embedding_prefix: str = "model.embed_tokens."
     final_norm_prefix: str = "model.norm."
     lm_head_prefix: str = "lm_head."
+    # positions of the schedule before whose layer the embedding output is added to the residual stream again
+    add_embedding_before: tuple = ()
 
 
 def require(d, key, typ):

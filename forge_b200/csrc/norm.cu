@@ -126,7 +126,41 @@ rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ w1, c
     }
 }
 
+// Layer norm with weight and bias:  y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b.  One CTA per row; the mean
+// first, then the mean of the squared deviations from it (not E[x^2] - mean^2), both with the fixed reduction tree.
+template <typename TOut>
+__global__ void __launch_bounds__(kNormThreads)
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, TOut* __restrict__ out,
+                 const int32_t* __restrict__ rows, int H, float eps) {
+    __shared__ float red[32];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    TOut* o = out + (size_t)r * H;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < H; c += kNormThreads) s += xr[c];
+    const float mean = forge::block_sum(s, red) / (float)H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += kNormThreads) {
+        const float d = xr[c] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv = 1.0f / sqrtf(forge::block_sum(ss, red) / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += kNormThreads) o[c] = forge::from_float<TOut>(fmaf((xr[c] - mean) * inv, w[c], b[c]));
+}
+
 }  // namespace
+
+extern "C" int forge_layernorm(const float* x, const float* w, const float* b, void* out, int out_dtype, const int32_t* rows, int R,
+                               int H, float eps, cudaStream_t stream) {
+    if (R < 0 || H <= 0) return forge::fail(FORGE_ERR_ARG, "layernorm: bad sizes R=%d H=%d", R, H);
+    if (R == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(out_dtype, TO,
+        e = forge::launch(layernorm_kernel<TO>, dim3(R), dim3(kNormThreads), 0, stream, 1, x, w, b, (TO*)out, rows, H, eps));
+    return forge::check_launch("layernorm", e);
+}
 
 extern "C" int forge_rmsnorm_pair(const float* x, const float* w1, const float* w2, void* out1, void* out2, int out_dtype, int R, int H,
                                   float eps, cudaStream_t stream) {

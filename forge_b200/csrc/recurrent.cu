@@ -8,6 +8,10 @@
 //   generalized delta rule:    S <- diag(w_t) S - (a_t * n_t) (n_t^T S) + k_t v_t^T ;   o_t = S^T r_t
 //                              n_t = k_t / sqrt(|k_t|^2 + 1e-6),  w_t = exp(-exp(-1/2) sigmoid(x_t + w0)),
 //                              a_t = sigmoid(y_t + a0)               (both terms read the state before the step)
+//   gated write (HGRN2):       S <- diag(f_t) S + (1 - f_t) v_t^T ;   o_t = S^T q_t          (no key: the forget gate also
+//                              f_t = l + (1 - l) sigmoid(x_t + b),  q_t = silu(y_t)            decides what is written)
+//
+// In the third the state is [K, V] with V value channels that need not equal K; the first two have V = K.
 //
 // A CTA per (request, head, 16 columns of S) walks the request's tokens of the step in order; column j of S (the K numbers
 // that meet value channel j) lives in the registers of eight neighbouring threads, so a token costs K/8 multiply-adds per
@@ -34,6 +38,7 @@ constexpr int kScanThreads = kSplit * kCols;
 // What the recurrence multiplies with, made in place from what the projections gave, for all tokens at once, a warp per
 // (token, head):   MODE 0: x <- exp(-exp(x + w0));
 //                  MODE 1: x <- exp(-exp(-1/2) sigmoid(x + w0)),  y <- sigmoid(y + a0),  inv[t, head] = 1 / (|k|^2 + 1e-6)
+//                  MODE 2: x <- a0 + (1 - a0) sigmoid(x + w0)  (a0: the gate's lower bound),  y <- y sigmoid(y)
 template <int MODE>
 __global__ void __launch_bounds__(128)
 scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld_y, const float* __restrict__ k, int ld_k,
@@ -53,6 +58,11 @@ scan_gates_kernel(float* __restrict__ x, int ld_x, float* __restrict__ y, int ld
         float* px = x + t * ld_x + c;
         if (MODE == 0) {
             *px = expf(-expf(*px + w0[c]));
+        } else if (MODE == 2) {
+            const float low = a0[c];
+            *px = low + (1.0f - low) * sigmoidf(*px + w0[c]);
+            float* py = y + t * ld_y + c;
+            *py = *py * sigmoidf(*py);
         } else {
             *px = expf(-0.6065306597126334f * sigmoidf(*px + w0[c]));
             float* py = y + t * ld_y + c;
@@ -73,7 +83,8 @@ __device__ __forceinline__ void stage_async(float* dst, const float* src, int by
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// MODE 0: decay and bonus; MODE 1: generalized delta rule.  d: the decays, a: the removal rates (MODE 1), both ready made
+// MODE 0: decay and bonus; MODE 1: generalized delta rule; MODE 2: gated write (no k: 1 - d stands for it; KV value
+// channels, the columns of S).  d: the decays, a: the removal rates (MODE 1), both ready made
 // (scan_gates_kernel).  last_in (MODE 0, may be null): the mixer's input rows [T, W] of the activation type; the
 // request's last row is kept as fp32 at state + prev_off (the next step's "previous token").
 //
@@ -88,7 +99,7 @@ __global__ void __launch_bounds__(kScanThreads)
 state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a, const float* __restrict__ bonus,
                   const float* __restrict__ inv, float* __restrict__ state, long long state_stride, const int32_t* __restrict__ q_start,
                   const int32_t* __restrict__ slots, float* __restrict__ out, const TA* __restrict__ last_in, int W,
-                  long long prev_off, int N, int K, int vec) {
+                  long long prev_off, int N, int K, int KV, int vec) {
     constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
     __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
     __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
@@ -96,12 +107,12 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
     forge::pdl_launch_dependents();
     const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, jl = tid / kSplit, q = tid % kSplit;
     const int j = blockIdx.z * kCols + jl;
-    const bool live = j < K;
-    const int col = head * K + j;
+    const bool live = j < KV;
+    const int col = head * KV + j;
     // channels beyond K stay zero in every staged vector: the copies never touch them
     for (int i = tid; i < 2 * kScanTokens * KMAX; i += kScanThreads) {
         (&rs[0][0][0])[i] = 0.f;
-        (&ks[0][0][0])[i] = 0.f;
+        if (MODE != 2) (&ks[0][0][0])[i] = 0.f;
         (&ds[0][0][0])[i] = 0.f;
         if (MODE == 1) (&as[0][0][0])[i] = 0.f;
     }
@@ -110,12 +121,12 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
     __syncthreads();
     forge::pdl_wait();
     const int t_lo = q_start[s], t_hi = q_start[s + 1];
-    float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * K;
+    float* S_g = state + (size_t)slots[s] * state_stride + (size_t)head * K * KV;
     // row of S that this thread's register ii holds
     auto row_of = [&](int ii) { return ((ii >> 2) * kSplit + q) * 4 + (ii & 3); };
     float S[RPT];
 #pragma unroll
-    for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && row_of(ii) < K) ? S_g[(size_t)row_of(ii) * K + j] : 0.f;
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = (live && row_of(ii) < K) ? S_g[(size_t)row_of(ii) * KV + j] : 0.f;
 
     const int piece = vec ? 4 : 1, pieces = K / piece;                   // a staged vector in pieces of 16 or 4 bytes
     auto fetch = [&](int buf, int tb) {
@@ -124,12 +135,12 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
             const int tt = p / pieces, ch = (p % pieces) * piece;
             const size_t t = (size_t)(tb + tt), c = (size_t)head * K + ch;
             stage_async(&rs[buf][tt][ch], r.p + t * r.ld + c, piece * 4);
-            stage_async(&ks[buf][tt][ch], k.p + t * k.ld + c, piece * 4);
+            if (MODE != 2) stage_async(&ks[buf][tt][ch], k.p + t * k.ld + c, piece * 4);
             stage_async(&ds[buf][tt][ch], d.p + t * d.ld + c, piece * 4);
             if (MODE == 1) stage_async(&as[buf][tt][ch], a.p + t * a.ld + c, piece * 4);
         }
         const int tt = tid / kCols, jc = blockIdx.z * kCols + tid % kCols;              // values: this CTA's columns only
-        if (tt < n && jc < K) stage_async(&vs[buf][tt][tid % kCols], v.p + (size_t)(tb + tt) * v.ld + head * K + jc, 4);
+        if (tt < n && jc < KV) stage_async(&vs[buf][tt][tid % kCols], v.p + (size_t)(tb + tt) * v.ld + head * KV + jc, 4);
         if (MODE == 1 && tid < n) stage_async(&is[buf][tid], inv + (size_t)(tb + tid) * N + head, 4);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -167,6 +178,19 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
                         S[ii] = fmaf(dv[e], S[ii], kv);
                     }
                 }
+            } else if (MODE == 2) {
+#pragma unroll
+                for (int c4 = 0; c4 < RPT / 4; ++c4) {
+                    const float4 rr = r4[c4 * kSplit], dd = d4[c4 * kSplit];
+                    const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, dv[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int ii = c4 * 4 + e;
+                        S[ii] = fmaf(dv[e], S[ii], (1.0f - dv[e]) * vj);
+                        if (e & 1) acc1 = fmaf(rv[e], S[ii], acc1);
+                        else acc0 = fmaf(rv[e], S[ii], acc0);
+                    }
+                }
             } else {
                 const float4* a4 = reinterpret_cast<const float4*>(&as[buf][tt][0]) + q;
                 float held0 = 0.f, held1 = 0.f;            // this thread's share of k^T S (its column)
@@ -200,14 +224,14 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
             float acc = acc0 + acc1;
 #pragma unroll
             for (int o = 1; o < kSplit; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && q == 0) out[(size_t)(tb + tt) * N * K + col] = acc;
+            if (live && q == 0) out[(size_t)(tb + tt) * N * KV + col] = acc;
         }
         __syncthreads();                                                  // before the next copies overwrite this half
     }
     if (live) {
 #pragma unroll
         for (int ii = 0; ii < RPT; ++ii)
-            if (row_of(ii) < K) S_g[(size_t)row_of(ii) * K + j] = S[ii];
+            if (row_of(ii) < K) S_g[(size_t)row_of(ii) * KV + j] = S[ii];
     }
     if (MODE == 0 && last_in != nullptr && t_hi > t_lo) {
         float* prev = state + (size_t)slots[s] * state_stride + prev_off;
@@ -240,11 +264,12 @@ token_shift_kernel(const TA* __restrict__ h, const float* __restrict__ state, lo
 }
 
 // One warp per (token, head): the head's K outputs divided by their root mean square, times a weight per channel,
-// times a gate (act 0: sigmoid(g), 1: g * sigmoid(g)), stored in the activation type for the output projection.
+// times a gate (act 0: sigmoid(g), 1: g * sigmoid(g), 2: no gate) and a number, stored in the activation type for the
+// output projection.  share_w: the K weights are shared by the heads.
 template <typename TA>
 __global__ void __launch_bounds__(128)
 head_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight, ScanInput g, TA* __restrict__ out, int rows,
-                   int N, int K, float eps, int act) {
+                   int N, int K, float eps, int act, float scale, int share_w) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -256,9 +281,12 @@ head_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight
     ss = forge::warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)K + eps);
     for (int c = lane; c < K; c += 32) {
-        const float gv = g.p[(size_t)t * g.ld + head * K + c];
-        const float gate = act == 1 ? gv * sigmoidf(gv) : sigmoidf(gv);
-        out[(size_t)t * N * K + head * K + c] = forge::from_float<TA>(src[c] * inv * weight[head * K + c] * gate);
+        float gate = scale;
+        if (act != 2) {
+            const float gv = g.p[(size_t)t * g.ld + head * K + c];
+            gate = scale * (act == 1 ? gv * sigmoidf(gv) : sigmoidf(gv));
+        }
+        out[(size_t)t * N * K + head * K + c] = forge::from_float<TA>(src[c] * inv * weight[share_w ? c : head * K + c] * gate);
     }
 }
 
@@ -275,11 +303,11 @@ __global__ void tanh_rows_kernel(ScanInput in, TA* __restrict__ out, int T, int 
 template <int MODE, typename TA>
 cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a,
                         const float* bonus, const float* inv, float* state, long long stride, const int32_t* q_start, const int32_t* slots,
-                        float* out, const TA* last_in, int W, long long prev_off, int N, int K, int vec) {
+                        float* out, const TA* last_in, int W, long long prev_off, int N, int K, int KV, int vec) {
 #define FORGE_SCAN_CASE(KM)                                                                                                  \
     case KM:                                                                                                                 \
         return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, inv, state, \
-                             stride, q_start, slots, out, last_in, W, prev_off, N, K, vec);
+                             stride, q_start, slots, out, last_in, W, prev_off, N, K, KV, vec);
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
         default: return cudaErrorInvalidValue;
@@ -289,7 +317,9 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
 
 }  // namespace
 
-// mode 0 (decay and bonus) / 1 (generalized delta rule).  r, k, v, x (and y, mode 1): fp32, row t at p + t * ld, head n's
+// mode 0 (decay and bonus) / 1 (generalized delta rule) / 2 (gated write: no k; x the forget gate's input with w0 its bias
+// and a0 its lower bound; y = r, which becomes silu(r) in place; v and out have N*KV columns, a head's state is [K, KV]).
+// KV = K in modes 0 and 1.  r, k, v, x (and y, mode 1): fp32, row t at p + t * ld, head n's
 // channels at columns n*K .. n*K+K-1; x (and y) are OVERWRITTEN with the decays (and removal rates) made from them; T: rows
 // of these matrices.  w0 (, a0, mode 1; bonus, mode 0): fp32 [N*K].  inv (mode 1): fp32 [T, N] scratch for 1 / (|k|^2 + 1e-6).  state: fp32 rows of state_stride
 // numbers, row slots[s] holds request s's N matrices [K, K] from its start.  out fp32 [T, N*K].  last_in (mode 0, optional):
@@ -298,21 +328,25 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
                                 const float* x, int ld_x, const float* y, int ld_y, const float* w0, const float* a0,
                                 const float* bonus, float* inv, float* state, long long state_stride, const int32_t* q_start,
                                 const int32_t* slots, float* out, const void* last_in, int last_dtype, int W, long long prev_off,
-                                int T, int S, int N, int K, cudaStream_t stream) {
-    if (T < 0 || S < 0 || N <= 0 || K <= 0 || (mode != 0 && mode != 1))
+                                int T, int S, int N, int K, int KV, cudaStream_t stream) {
+    if (T < 0 || S < 0 || N <= 0 || K <= 0 || KV <= 0 || mode < 0 || mode > 2 || (mode != 2 && KV != K))
         return forge::fail(FORGE_ERR_ARG, "state_scan: bad sizes S=%d N=%d K=%d mode=%d", S, N, K, mode);
     if (K > 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "state_scan: heads of %d channels (at most 128)", K);
-    if (state_stride < (long long)N * K * K) return forge::fail(FORGE_ERR_ARG, "state_scan: state rows are too short");
+    if (state_stride < (long long)N * K * KV) return forge::fail(FORGE_ERR_ARG, "state_scan: state rows are too short");
     if (mode == 0 && !bonus) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 0 needs the bonus");
     if (mode == 1 && (!y || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs the removal rate");
+    if (mode == 2 && (y != r || ld_y != ld_r || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 2 takes y = r and the gate's lower bound");
     if (S == 0) return FORGE_OK;
     const int kmax = (K + 31) / 32 * 32;
-    const dim3 grid(S, N, (K + kCols - 1) / kCols);
+    const dim3 grid(S, N, (KV + kCols - 1) / kCols);
     // decays (and removal rates, and the unit keys' divisors) for all tokens at once, in place
     {
         if (mode == 1 && !inv) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs room for the keys' divisors");
         const unsigned blocks = (unsigned)(((size_t)T * N + 3) / 4);
-        cudaError_t g = mode == 0
+        cudaError_t g = mode == 2
+            ? forge::launch(scan_gates_kernel<2>, dim3(blocks), dim3(128), 0, stream, 1, const_cast<float*>(x), ld_x, const_cast<float*>(y), ld_y,
+                            (const float*)nullptr, 0, (float*)nullptr, w0, a0, T, N, K)
+            : mode == 0
             ? forge::launch(scan_gates_kernel<0>, dim3(blocks), dim3(128), 0, stream, 1, const_cast<float*>(x), ld_x, (float*)nullptr, 0,
                             (const float*)nullptr, 0, (float*)nullptr, w0, a0, T, N, K)
             : forge::launch(scan_gates_kernel<1>, dim3(blocks), dim3(128), 0, stream, 1, const_cast<float*>(x), ld_x, const_cast<float*>(y), ld_y,
@@ -323,14 +357,16 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
     auto aligned = [](const float* p, int ld) { return p == nullptr || (((uintptr_t)p & 15) == 0 && ld % 4 == 0); };
     const int vec = (K % 4 == 0 && aligned(r, ld_r) && aligned(k, ld_k) && aligned(x, ld_x) && aligned(y, ld_y)) ? 1 : 0;
     cudaError_t e;
-    if (mode == 1) {
-        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, nullptr, inv, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, vec);
+    if (mode == 2) {
+        e = launch_scan<2, float>(kmax, grid, stream, R, R, V, X, Y, nullptr, nullptr, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, KV, vec);
+    } else if (mode == 1) {
+        e = launch_scan<1, float>(kmax, grid, stream, R, Kk, V, X, Y, nullptr, inv, state, state_stride, q_start, slots, out, nullptr, 0, 0, N, K, K, vec);
     } else if (last_in == nullptr || last_dtype == FORGE_F32) {
         e = launch_scan<0, float>(kmax, grid, stream, R, Kk, V, X, Y, bonus, nullptr, state, state_stride, q_start, slots, out,
-                                  (const float*)last_in, W, prev_off, N, K, vec);
+                                  (const float*)last_in, W, prev_off, N, K, K, vec);
     } else {
         e = launch_scan<0, __nv_bfloat16>(kmax, grid, stream, R, Kk, V, X, Y, bonus, nullptr, state, state_stride, q_start, slots, out,
-                                          (const __nv_bfloat16*)last_in, W, prev_off, N, K, vec);
+                                          (const __nv_bfloat16*)last_in, W, prev_off, N, K, K, vec);
     }
     return forge::check_launch("state_scan", e);
 }
@@ -350,15 +386,15 @@ extern "C" int forge_token_shift(const void* h, const float* state, long long st
 
 // o fp32 [T, N*K]; weight fp32 [N*K]; g fp32 rows of ld_g (the gate before its activation); out of type dtype [T, N*K].
 extern "C" int forge_head_finish(const float* o, const float* weight, const float* g, int ld_g, void* out, int dtype, int T, int N,
-                                 int K, float eps, int act, cudaStream_t stream) {
-    if (T < 0 || N <= 0 || K <= 0 || (act != 0 && act != 1)) return forge::fail(FORGE_ERR_ARG, "head_finish: bad sizes T=%d N=%d K=%d", T, N, K);
+                                 int K, float eps, int act, float scale, int share_w, cudaStream_t stream) {
+    if (T < 0 || N <= 0 || K <= 0 || act < 0 || act > 2 || (act != 2 && !g)) return forge::fail(FORGE_ERR_ARG, "head_finish: bad sizes T=%d N=%d K=%d", T, N, K);
     if (T == 0) return FORGE_OK;
     if ((long long)T * N > 0x7fffffffLL / 2) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_finish: too many rows");
     const unsigned blocks = (unsigned)(((long long)T * N + 3) / 4);
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
         e = forge::launch(head_finish_kernel<TT>, dim3(blocks), dim3(128), 0, stream, 1, o, weight, ScanInput{g, ld_g}, (TT*)out, T, N, K,
-                          eps, act));
+                          eps, act, scale, share_w));
     return forge::check_launch("head_finish", e);
 }
 

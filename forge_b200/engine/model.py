@@ -27,6 +27,9 @@ class Model:
         for i in plan.schedule:
             if not 0 <= i < n:
                 raise ConfigError(f"schedule names layer {i}, the plan has {n} layers")
+        for pos in plan.add_embedding_before:
+            if not 0 <= pos < len(plan.schedule):
+                raise ConfigError(f"the embedding is to be added before run {pos}, the schedule has {len(plan.schedule)} runs")
         for i, spec in enumerate(plan.layers):
             if spec.cache_from is not None and not 0 <= spec.cache_from < n:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
@@ -113,7 +116,7 @@ class Model:
         from .. import kernels
         self._fused = None
         sched = self.plan.schedule
-        if self.rt.full_precision or not sched or sched != list(range(len(self.blocks))):
+        if self.rt.full_precision or not sched or sched != list(range(len(self.blocks))) or self.plan.add_embedding_before:
             return False
         descs = [b.fused_decode() if hasattr(b, "fused_decode") else None for b in self.blocks]
         if any(d is None for d in descs):
@@ -170,7 +173,13 @@ class Model:
         else:
             ws = workspace
             replay = None
+            again = self.plan.add_embedding_before
             for pos, i in enumerate(self.plan.schedule):
+                if pos in again:
+                    # a repeated pass starts from the stream plus the embedding output: the table's rows are gathered
+                    # once more and added, which is the same numbers as a kept copy and needs no room for one
+                    self.embedding.forward(batch.token_ids, status=batch.status, add_into=residual)
+                    replay = None
                 if replay is not None:
                     replay.run(self._replay_tensors[pos] + [position_caches[pos].kv])
                     continue

@@ -32,7 +32,9 @@ _P, _I, _F, _LL = c_void_p, c_int, c_float, ctypes.c_longlong
 
 _SIGNATURES = {
     "core": {
-        "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P],
+        "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _I, _P, _P],
+        "forge_layernorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "forge_act_rows": [_P, _I, _P, _I, _I, _I, _I, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "forge_rmsnorm_pair": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
         "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -64,9 +66,11 @@ _SIGNATURES = {
         "forge_headmix_attention": [_P] * 10 + [_I] * 7 + [_LL, _I, _I, _I, _F, _I, _I, _P],
         "forge_headmix_mma_supports": [_I, _I, _I, _I, _I],
         "forge_headmix_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
-        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _P],
+        "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _I, _P],
+        "forge_scored_prepare": [_P, _I] + [_P] * 7 + [_I] * 8 + [_F, _F, _F, _I, _LL, _P],
+        "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-        "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
+        "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
     },
     "decode_layers": {
@@ -84,7 +88,8 @@ _libs = {}
 # tested before use, a bad one raises bit 4 of the step's status word and is skipped.  The entries that tell a
 # library the bounds, per library (one per source file that checks):
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
-                  "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma"],
+                  "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma",
+                             "forge_checks_configure_attention_scored"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -502,15 +507,18 @@ def new_ints(values, device):
 
 # ---------------------------------------------------------------------------------------------- core
 
-def embedding(ids, table, out=None, status=None, scale=1.0):
-    """out[t,:] = table[ids[t],:] * scale as float32 [T,H]; ids int32 [T]; table [V,H] float32 or bfloat16."""
+def embedding(ids, table, out=None, status=None, scale=1.0, add=False):
+    """out[t,:] = table[ids[t],:] * scale as float32 [T,H]; ids int32 [T]; table [V,H] float32 or bfloat16.  ``add``: the rows
+    are added to ``out`` instead."""
+    if add and out is None:
+        raise KernelError("embedding: nothing to add to")
     lib = library("core")
     T, (V, H) = ids.numel(), table.shape
     if out is None:
         out = new_tensor((T, H), torch.float32, table.device)
     _check(lib, lib.forge_embedding(_need(ids, "ids", torch.int32), _need(table, "table", ndim=2),
                                     dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V, float(scale),
-                                    _opt(status, "status", torch.int32), _stream()), "embedding")
+                                    1 if add else 0, _opt(status, "status", torch.int32), _stream()), "embedding")
     return out
 
 
@@ -526,6 +534,33 @@ def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
     _check(lib, lib.forge_rmsnorm(_need(x, "x", torch.float32, 2), _need(weight, "weight", torch.float32),
                                   _need(out, "out", out_dtype), dtype_code(out_dtype),
                                   _opt(rows, "rows", torch.int32), R, H, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def layernorm(x, weight, bias, eps, out_dtype, rows=None):
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b over the last dim of float32 x [T,H]; ``rows`` (int32) picks rows."""
+    lib = library("core")
+    H = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    if weight.numel() != H or bias.numel() != H:
+        raise KernelError(f"layernorm: weight and bias have {weight.numel()} and {bias.numel()} elements, rows have {H}")
+    out = new_tensor((R, H), out_dtype, x.device)
+    _check(lib, lib.forge_layernorm(_need(x, "x", torch.float32, 2), _need(weight, "weight", torch.float32),
+                                    _need(bias, "bias", torch.float32), _need(out, "out", out_dtype), dtype_code(out_dtype),
+                                    _opt(rows, "rows", torch.int32), R, H, float(eps), _stream()), "layernorm")
+    return out
+
+
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def act_rows(x, out_dtype, activation):
+    """activation(x) of float32 x [T,n] in ``out_dtype``: "gelu" (the exact one, with erf), "gelu_tanh", "silu"."""
+    lib = library("core")
+    T, n = x.shape
+    out = new_tensor((T, n), out_dtype, x.device)
+    _check(lib, lib.forge_act_rows(_need(x, "x", torch.float32, 2), n, _need(out, "out", out_dtype), dtype_code(out_dtype), T, n,
+                                   ACTIVATIONS[activation], _stream()), "act_rows")
     return out
 
 
@@ -799,6 +834,67 @@ def headmix_attention(q, cache, group_batch, batch, H, G, D, E, page_size, scale
     return out
 
 
+SCORED_KEYS_PER_CHUNK = 64          # fixed: a token's sums must not depend on the step's shape
+
+
+def scored_tile_tokens(H, G, M, D, E, single_tokens=False):
+    """Tokens per tile of the scored attention for these sizes: the most that fit a CTA's shared memory."""
+    if single_tokens:
+        return 1
+    R, KT = H // G, SCORED_KEYS_PER_CHUNK
+    for TQ in (16, 8, 4, 2, 1):
+        if 4 * (TQ * R * M * (D + E + KT + 3) + KT * (M * D + 1 + E)) <= HEADMIX_SMEM_LIMIT:
+            return TQ
+    raise KernelError(f"scored attention: {H // G} heads of {M}x{D}/{E} channels do not fit a CTA's shared memory")
+
+
+def scored_prepare(proj, positions, slot_mapping, cache, H, G, M, D, E, page_size, act_dtype, inv_freq=None, q_norm=None,
+                   k_norm=None, eps=0.0, temp_coef=0.0, temp_every=0.0):
+    """proj fp32 [T, >= (H+G)*M*D + G*E] = [q | k | v] of a step's tokens: optionally an RMS norm over all of a token's query
+    channels (weights ``q_norm`` fp32 [H*M*D]) and over all its key channels (``k_norm``), a rotation of the first
+    2*len(inv_freq) channels of every map of D channels (channel i with i + half), a query temperature
+    1 + temp_coef ln(floor((p+1)/temp_every) + 1); k and v go to ``slot_mapping`` in ``cache`` (None: no write); returns q
+    [T, H*M*D] in ``act_dtype``."""
+    lib = library("mixers")
+    T, ld = proj.shape
+    q = new_tensor((T, H * M * D), act_dtype, proj.device)
+    if cache is not None and cache.dtype != act_dtype:
+        raise KernelError("scored_prepare: cache and activation dtypes differ")
+    if cache is None:
+        slot_mapping = None
+    stride = _page_stride(cache) if cache is not None else G * page_size * (M * D + E)
+    rot = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _check(lib, lib.forge_scored_prepare(
+        _need(proj, "proj", torch.float32, 2), ld, _need(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _opt(inv_freq, "inv_freq", torch.float32) if rot else None, _opt(q_norm, "q_norm", torch.float32), _opt(k_norm, "k_norm", torch.float32),
+        _need(q, "q", act_dtype), _opt(cache, "cache"), dtype_code(act_dtype), T, H * M, G * M, G, D, E, rot, float(eps), float(temp_coef),
+        float(temp_every), page_size, stride, _stream()), "scored_prepare")
+    return q
+
+
+def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, scale, r1=None, r2=None, lam=0.0, post=1.0, eps=0.0,
+                     out_scale=1.0):
+    """Causal softmax attention of every token of the step over its request's pages, M maps per head (see
+    csrc/attention_scored.cu): scores scale q.k - r1_h ln(1 + r2_h (i - j)); with M = 2 the maps' outputs are combined as
+    a1 - lam a2, divided by their root mean square (``eps`` inside the root) and multiplied by ``post``.  Returns [T, H*E] in
+    q's type, times ``out_scale``."""
+    lib = library("mixers")
+    T = q.shape[0]
+    single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
+    TQ = scored_tile_tokens(H, G, M, D, E, single_tokens=single)
+    t0, tn, tiles = headmix_plan(batch, TQ, q.device)
+    out = new_tensor((T, H * E), q.dtype, q.device)
+    if cache.dtype != q.dtype:
+        raise KernelError("scored_attention: q and cache dtypes differ")
+    _check(lib, lib.forge_scored_attention(
+        _need(q, "q", ndim=2), _need(cache, "cache"), _need(group_batch.block_table, "block_table", torch.int32, 2),
+        _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+        _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _need(out, "out", q.dtype),
+        dtype_code(q.dtype), tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1], float(scale),
+        float(lam), float(post), float(eps), float(out_scale), TQ, SCORED_KEYS_PER_CHUNK, _stream()), "scored_attention")
+    return out
+
+
 def _cols(t, off=0):
     """(pointer, leading dimension) of the columns of fp32 matrix ``t`` from ``off`` on."""
     if t is None:
@@ -806,27 +902,30 @@ def _cols(t, off=0):
     return _need(t, "matrix", torch.float32, 2) + 4 * int(off), t.shape[1]
 
 
-STATE_SCANS = {"decay_bonus": 0, "delta": 1}
+STATE_SCANS = {"decay_bonus": 0, "delta": 1, "gated_write": 2}
 
 
-def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=None, last_in=None, prev_off=0):
+def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=None, last_in=None, prev_off=0, KV=None):
     """The recurrence of a mixer with a [K, K] state per head (``kind``: "decay_bonus" or "delta", see csrc/recurrent.cu)
     over the step's tokens, request by request, from and into ``state`` fp32 [slots, row].  r, k, v, x, y: (fp32 matrix,
     first column) pairs with N*K columns from there; x (and y) are overwritten with the decays (and removal rates) made from
     them; returns fp32 [T, N*K].  ``last_in`` ("decay_bonus"): the mixer's input
-    [T, W], whose last row per request is kept in the state row at ``prev_off``."""
+    [T, W], whose last row per request is kept in the state row at ``prev_off``.
+    "gated_write": no k (None); x is the forget gate's input, w0 its bias, a0 its lower bound; r becomes silu(r) in place; v
+    has N*KV columns and so has the result; a head's state is [K, KV]."""
     lib = library("mixers")
     T = r[0].shape[0]
-    out = new_tensor((T, N * K), torch.float32, r[0].device)
-    (rp, rl), (kp, kl), (vp, vl), (xp, xl) = _cols(*r), _cols(*k), _cols(*v), _cols(*x)
-    yp, yl = _cols(*y) if y is not None else (None, 0)
+    KV = K if KV is None else int(KV)
+    out = new_tensor((T, N * KV), torch.float32, r[0].device)
+    (rp, rl), (kp, kl), (vp, vl), (xp, xl) = _cols(*r), _cols(*k) if k is not None else (None, 0), _cols(*v), _cols(*x)
+    yp, yl = _cols(*y) if y is not None else ((rp, rl) if kind == "gated_write" else (None, 0))
     W = last_in.shape[1] if last_in is not None else 0
     inv = new_tensor((T, N), torch.float32, r[0].device) if kind == "delta" else None       # the unit keys' divisors
     _check(lib, lib.forge_state_scan(
         STATE_SCANS[kind], rp, rl, kp, kl, vp, vl, xp, xl, yp, yl, _need(w0, "w0", torch.float32), _opt(a0, "a0", torch.float32),
         _opt(bonus, "bonus", torch.float32), _opt(inv, "inv", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
         _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(out, "out", torch.float32),
-        _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), T, batch.num_requests, N, K,
+        _opt(last_in, "last_in"), dtype_code(last_in.dtype) if last_in is not None else 0, W, int(prev_off), T, batch.num_requests, N, K, KV,
         _stream()), "state_scan")
     count_launches(1)              # the kernel that makes the decays (and removal rates) from x (and y), in place
     return out
@@ -846,19 +945,23 @@ def token_shift(h, state, prev_off, batch, mu):
     return out
 
 
-HEAD_GATES = {"sigmoid": 0, "silu": 1}
+HEAD_GATES = {"sigmoid": 0, "silu": 1, "none": 2}
 
 
-def head_finish(o, weight, gate, N, K, eps, gate_activation, out_dtype):
-    """o fp32 [T, N*K]: every head divided by its root mean square (eps inside the root), times ``weight`` fp32 [N*K], times
-    the activation of ``gate`` ((fp32 matrix, first column)); [T, N*K] in ``out_dtype``."""
+def head_finish(o, weight, gate, N, K, eps, gate_activation, out_dtype, scale=1.0):
+    """o fp32 [T, N*K]: every head divided by its root mean square (eps inside the root), times ``weight`` fp32 [N*K] (or [K],
+    shared by the heads), times the activation of ``gate`` ((fp32 matrix, first column); None with "none"), times ``scale``;
+    [T, N*K] in ``out_dtype``."""
     lib = library("mixers")
     T = o.shape[0]
     out = new_tensor((T, N * K), out_dtype, o.device)
-    gp, gl = _cols(*gate)
+    gp, gl = _cols(*gate) if gate is not None else (None, 0)
+    if weight.numel() not in (K, N * K):
+        raise KernelError(f"head_finish: {weight.numel()} weights for {N} heads of {K}")
+    share = 1 if (weight.numel() == K and N > 1) else 0
     _check(lib, lib.forge_head_finish(_need(o, "o", torch.float32, 2), _need(weight, "weight", torch.float32), gp, gl,
                                       _need(out, "out", out_dtype), dtype_code(out_dtype), T, N, K, float(eps),
-                                      HEAD_GATES[gate_activation], _stream()), "head_finish")
+                                      HEAD_GATES[gate_activation], float(scale), share, _stream()), "head_finish")
     return out
 
 

@@ -7,7 +7,7 @@ the model configuration or at other layers.  Categories and the interface of eac
   norm          forward(x_f32[T,H], out_dtype, rows=None) -> [R,H]
   position      encode_and_store(qkv_f32, positions, slot_mapping, kv_cache, num_heads, num_kv_heads,
                                  page_size, batch=None) -> q[T,NH*HD]
-  mixer         cache_spec() -> KVCacheSpec | StateSpec | None
+  mixer         cache_spec() -> KVCacheSpec | StateSpec | CompositeCacheSpec | None
                 forward(x[T,H], batch, cache, residual_f32[T,H])      (adds its output into residual)
   feed_forward  forward(x[T,H], residual_f32[T,H])                     (adds its output into residual)
   block         built from a LayerSpec; forward(residual, batch, cache)
@@ -61,6 +61,13 @@ class StateSpec:
     """A mixer that keeps per-request state of fixed size: one row of ``shape`` per request slot."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeCacheSpec:
+    """A mixer made of several mixers that each keep something: one spec (or None) per inner mixer, in order.  The mixer
+    then gets a cache whose ``parts`` are the inner mixers' caches."""
+    parts: Tuple[object, ...]
 
 
 def register_part(category, kind, cls, replace=False):

@@ -1,6 +1,6 @@
 """Arrangements of a layer's parts around the fp32 residual stream.
 
-"pre_norm":  r += mixer(norm_in(r));  r += feed_forward(norm_post(r))
+"pre_norm":  r += mixer(norm_in(r));  r += feed_forward(norm_post(r))     (a layer without feed-forward has one norm)
 (reference: src/inference/engines/generic_engine.cpp:931-938, 1045-1052, 1080).
 "parallel":  r += mixer(norm_a(r)) + feed_forward(norm_b(r)), both branches of the same r.  The additions happen in
 the epilogue of each part's last matrix product, in fp32.
@@ -13,7 +13,7 @@ class PreNormBlock(Part):
     graph_safe = True       # the arrangement itself looks at nothing of the step; its parts answer for themselves
 
     def sub_parts(self):
-        return [self.mixer, self.feed_forward, self.norm_in, self.norm_post]
+        return [p for p in (self.mixer, self.feed_forward, self.norm_in, self.norm_post) if p is not None]
     NORM_NAMES = {"input": "input_layernorm.", "post_mixer": "post_attention_layernorm."}
 
     def __init__(self, rt, layer_spec):
@@ -21,11 +21,13 @@ class PreNormBlock(Part):
         self.mixer = build_part("mixer", layer_spec.mixer, rt)
         self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
         self.norm_in = build_part("norm", layer_spec.norms["input"], rt)
-        self.norm_post = build_part("norm", layer_spec.norms["post_mixer"], rt)
+        post = layer_spec.norms.get("post_mixer")
+        self.norm_post = None if post is None else build_part("norm", post, rt)
+        self.norm_prefixes = {**self.NORM_NAMES, **(layer_spec.norm_prefixes or {})}
 
     def _children(self):
-        return [("", self.mixer), ("", self.feed_forward), (self.NORM_NAMES["input"], self.norm_in),
-                (self.NORM_NAMES["post_mixer"], self.norm_post)]
+        out = [("", self.mixer), ("", self.feed_forward), (self.norm_prefixes["input"], self.norm_in)]
+        return out if self.norm_post is None else out + [(self.norm_prefixes["post_mixer"], self.norm_post)]
 
     def tensor_specs(self):
         specs = {}
@@ -46,7 +48,7 @@ class PreNormBlock(Part):
         from .feedforward import SwiGLU
         from .norm import RMSNorm
         m, f, n1, n2 = self.mixer, self.feed_forward, self.norm_in, self.norm_post
-        if type(self) is not PreNormBlock or type(m) is not GQAAttention or type(f) is not SwiGLU \
+        if n2 is None or type(self) is not PreNormBlock or type(m) is not GQAAttention or type(f) is not SwiGLU \
                 or type(n1) is not RMSNorm or type(n2) is not RMSNorm or self.rt.full_precision:
             return None
         pos = m.position.fused_decode() if hasattr(m.position, "fused_decode") else None
@@ -62,6 +64,8 @@ class PreNormBlock(Part):
 
     def _replay_parts(self):
         from .base import replay_of
+        if self.norm_post is None:
+            return None
         parts = [replay_of(p) for p in (self.norm_in, self.mixer, self.norm_post, self.feed_forward)]
         return None if type(self) is not PreNormBlock or any(p is None for p in parts) else parts
 
@@ -76,8 +80,9 @@ class PreNormBlock(Part):
     def forward(self, residual, batch, cache):
         x = self.norm_in.forward(residual)
         self.mixer.forward(x, batch, cache, residual)
-        x = self.norm_post.forward(residual)
-        self.feed_forward.forward(x, residual)
+        if self.norm_post is not None:
+            x = self.norm_post.forward(residual)
+            self.feed_forward.forward(x, residual)
 
 
 class ParallelBlock(Part):

@@ -27,8 +27,9 @@ class TokenEmbedding(Part):
         """The table as an output head reads it when the two are tied: [vocab, hidden] in the compute dtype."""
         return self.table
 
-    def forward(self, token_ids, status=None):
-        return kernels.embedding(token_ids, self.table, status=status, scale=self.scale)
+    def forward(self, token_ids, status=None, add_into=None):
+        """The tokens' rows as a new fp32 stream, or (``add_into``) added to an existing one."""
+        return kernels.embedding(token_ids, self.table, out=add_into, status=status, scale=self.scale, add=add_into is not None)
 
 
 class LMHead(Part):

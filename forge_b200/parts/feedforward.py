@@ -50,6 +50,33 @@ class GeGLU(SwiGLU):
     activation = "geglu"
 
 
+class DenseFeedForward(Part):
+    """Ungated feed-forward:  residual += act(x.Wu^T) . Wd^T; ``activation``: "gelu" (the exact one, with erf),
+    "gelu_tanh" or "silu"; ``names``: the two matrices' tensor names."""
+    graph_safe = True
+
+    def __init__(self, rt, hidden_size, intermediate_size, activation="gelu", names=None):
+        from .. import kernels
+        if activation not in kernels.ACTIVATIONS:
+            from ..config.base import ConfigError
+            raise ConfigError(f"feed-forward activation must be one of {sorted(kernels.ACTIVATIONS)}, got {activation!r}")
+        self.rt, self.hidden_size, self.intermediate_size, self.activation = rt, hidden_size, intermediate_size, activation
+        self.names = {"up": "mlp.up", "down": "mlp.down", **(names or {})}
+        self.up = self.down = None
+
+    def tensor_specs(self):
+        n, H, I = self.names, self.hidden_size, self.intermediate_size
+        return {n["up"]: TensorSpec((I, H)), n["down"]: TensorSpec((H, I))}
+
+    def bind(self, tensors):
+        self.up = Linear(self._matrix(tensors[self.names["up"]]), None, self.rt)
+        self.down = Linear(self._matrix(tensors[self.names["down"]]), None, self.rt)
+
+    def forward(self, x, residual):
+        act = self.up.forward(x, epilogue=self.activation)          # [T,I] in the activation type
+        self.down.forward(act, accumulate_into=residual)
+
+
 class NoFeedForward(Part):
     """A layer without a feed-forward: adds nothing."""
     graph_safe = True
@@ -63,4 +90,5 @@ class NoFeedForward(Part):
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
 register_part("feed_forward", "geglu", GeGLU, replace=True)
+register_part("feed_forward", "dense", DenseFeedForward, replace=True)
 register_part("feed_forward", "none", NoFeedForward, replace=True)

@@ -29,7 +29,11 @@ class Linear:
         epilogue "swiglu": rt.dtype [M,N/2], out[:,j] = silu(y[:,2j]) * y[:,2j+1]
         epilogue "geglu":  the same with the tanh form of gelu as the gate's activation
         epilogue "cast":   rt.dtype [M,N]
+        epilogue "gelu" | "gelu_tanh" | "silu":  rt.dtype [M,N], the activation of every element
         """
+        if epilogue in kernels.ACTIVATIONS:
+            y = kernels.gemm_sm100(x, self.weight, bias=self.bias) if self.tensor_core else kernels.gemm_simt(x, self.weight, bias=self.bias)
+            return kernels.act_rows(y, self.rt.dtype, epilogue)
         if self.tensor_core:
             return kernels.gemm_sm100(x, self.weight, bias=self.bias, accumulate_into=accumulate_into, epilogue=epilogue)
         if epilogue == "none":

@@ -1,4 +1,5 @@
-"""RMSNorm:  y = x * rsqrt(mean(x^2) + eps) * w   (reference: src/operators/cuda/cuda_rms_norm.cu:10-36)."""
+"""RMSNorm:  y = x * rsqrt(mean(x^2) + eps) * w   (reference: src/operators/cuda/cuda_rms_norm.cu:10-36).
+LayerNorm:  y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b."""
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import Part, register_part
@@ -28,4 +29,26 @@ class RMSNorm(Part):
         return kernels.rmsnorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)
 
 
+class LayerNorm(Part):
+    """Layer norm with a weight and a bias per channel; ``names``: the two tensors' names."""
+    graph_safe = True
+
+    def __init__(self, rt, size, eps, names=None):
+        self.rt, self.size, self.eps = rt, int(size), float(eps)
+        self.names = {"weight": "weight", "bias": "bias", **(names or {})}
+        self.weight = self.bias = None
+
+    def tensor_specs(self):
+        return {self.names["weight"]: TensorSpec((self.size,), role="norm"), self.names["bias"]: TensorSpec((self.size,), role="bias")}
+
+    def bind(self, tensors):
+        self.weight = self._vector_f32(tensors[self.names["weight"]])
+        self.bias = self._vector_f32(tensors[self.names["bias"]])
+
+    def forward(self, x, out_dtype=None, rows=None):
+        """x: fp32 [T,size] (the residual stream); returns [T or len(rows), size] in ``out_dtype``."""
+        return kernels.layernorm(x, self.weight, self.bias, self.eps, out_dtype or self.rt.dtype, rows=rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+register_part("norm", "layernorm", LayerNorm, replace=True)

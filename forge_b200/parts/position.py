@@ -87,6 +87,12 @@ class PairedRotary(Part):
         self.inv_freq = freq.to(torch.float32).to(rt.device)
 
 
+class SplitHalfRotary(PairedRotary):
+    """The same frequencies, but channel i of the first ``rotary_dims`` channels is paired with channel i + rotary_dims/2
+    (the rest pass unchanged).  Like its base it only keeps ``inv_freq``; the mixer's prepare step rotates."""
+
+
 register_part("position", "rope", RotaryEmbedding, replace=True)
+register_part("position", "rope_halves", SplitHalfRotary, replace=True)
 register_part("position", "rope_pairs", PairedRotary, replace=True)
 register_part("position", "none", NoPosition, replace=True)

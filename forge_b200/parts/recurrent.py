@@ -12,6 +12,11 @@ output by its root mean square, multiply by a weight per channel and by a gate, 
     S <- diag(w_t) S - (a_t * n_t)(n_t^T S) + k_t v_t^T;   o_t = S^T r_t
 
 The rank of the decay's projection is read from the file's tensors (``rank`` is only what random weights take).
+
+"gated_write" (HGRN2; N heads of K key and V value channels, state [K, V], no key and no low-rank decay):
+    q_t = silu(Wq h);  f_t = l + (1 - l) sigmoid(Wf h + b)  (l: a lower bound per channel);  v_t = Wv h
+    S <- diag(f_t) S + (1 - f_t) v_t^T;   o_t = S^T q_t;   every head's o divided by its root mean square, times a weight per
+    value channel that the heads share; projected back.  ``out_scale`` multiplies the mixer's output.
 """
 import torch
 
@@ -122,5 +127,46 @@ class GeneralDeltaMixer(_StateMixer):
         self.o.forward(y, accumulate_into=residual)
 
 
+class GatedWriteMixer(Part):
+    graph_safe = True       # request boundaries and state rows come from the batch's device tensors (q_start, slots)
+
+    def __init__(self, rt, hidden_size, num_heads, head_dim, eps, v_head_dim=None, out_scale=1.0, prefix="mix."):
+        if head_dim > 128:
+            raise ConfigError(f"state mixers take heads of up to 128 key channels, not {head_dim}")
+        self.rt, self.hidden_size, self.num_heads, self.head_dim = rt, hidden_size, num_heads, head_dim
+        self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
+        self.eps, self.out_scale, self.prefix = float(eps), float(out_scale), prefix
+
+    def _n(self, short):
+        return self.prefix + short
+
+    def tensor_specs(self):
+        W, NK, NV = self.hidden_size, self.num_heads * self.head_dim, self.num_heads * self.v_head_dim
+        return {self._n("q"): TensorSpec((NK, W)), self._n("f"): TensorSpec((NK, W)), self._n("f.b"): TensorSpec((NK,), role="bias"),
+                self._n("lower"): TensorSpec((NK,), role="fraction"), self._n("v"): TensorSpec((NV, W)),
+                self._n("norm"): TensorSpec((self.v_head_dim,), role="norm"), self._n("o"): TensorSpec((W, NV))}
+
+    def bind(self, tensors):
+        # q, f and v read the same input: one product
+        self.proj = Linear(self._matrix(torch.cat([tensors[self._n(m)] for m in ("q", "f", "v")], dim=0)), None, self.rt)
+        self.f_bias = self._vector_f32(tensors[self._n("f.b")])
+        self.lower = self._vector_f32(tensors[self._n("lower")])
+        self.norm = self._vector_f32(tensors[self._n("norm")])
+        self.o = Linear(self._matrix(tensors[self._n("o")]), None, self.rt)
+
+    def cache_spec(self):
+        return StateSpec((self.num_heads * self.head_dim * self.v_head_dim,), torch.float32)
+
+    def forward(self, x, batch, cache, residual):
+        N, K, V = self.num_heads, self.head_dim, self.v_head_dim
+        NK = N * K
+        p = self.proj.forward(x)                                     # fp32 [T, 2*N*K + N*V]: q | f | v
+        o = kernels.state_scan("gated_write", (p, 0), None, (p, 2 * NK), (p, NK), self.f_bias, cache.state, batch, N, K,
+                               a0=self.lower, KV=V)
+        y = kernels.head_finish(o, self.norm, None, N, V, self.eps, "none", self.rt.dtype, scale=self.out_scale)
+        self.o.forward(y, accumulate_into=residual)
+
+
+register_part("mixer", "gated_write", GatedWriteMixer, replace=True)
 register_part("mixer", "wkv", WKVMixer, replace=True)
 register_part("mixer", "general_delta", GeneralDeltaMixer, replace=True)

@@ -1,0 +1,136 @@
+"""Two causal softmax attentions whose scores are shaped before the softmax, both on the paged cache and on the same
+kernels (``kernels.scored_prepare`` / ``kernels.scored_attention``); query/key heads and value heads may differ in size.
+
+"differential_attention": every head has two maps (q and k carry two vectors of D channels per head, [map 1 | map 2]),
+each a softmax of its own over the same values; with a_1, a_2 the maps' outputs
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff              (one number for the layer)
+    o = a_1 - lambda a_2;   o <- o / sqrt(mean(o^2) + eps) * (1 - diff)
+Rotary positions on the first ``rotary_dims`` channels of every map, channel i paired with i + rotary_dims/2.
+
+"distance_attention": no rotation; biases in every projection; an RMS norm over ALL query channels of a token (and all
+key channels) with a weight per channel; a query temperature 1 + coef ln(floor((p + 1) / every) + 1) at position p; and
+    score(i, j) = scale q(i) . k(j) - r1_h ln(1 + r2_h (i - j))
+
+``out_scale`` multiplies the mixer's output (a mixer that runs beside another with weights of their own).
+"""
+import math
+
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError
+from ..weights.loader import TensorSpec
+from .base import KVCacheSpec, Part, build_part, register_part
+from .linear import Linear
+
+
+class _ScoredAttention(Part):
+    graph_safe = True       # positions, tables, slots and request boundaries are read from the batch's device tensors
+    MAPS = 1
+
+    def _sizes(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, scale, out_scale, prefix):
+        if num_heads % num_kv_heads:
+            raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} key/value heads")
+        self.rt, self.hidden_size = rt, hidden_size
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.out_scale, self.prefix = float(out_scale), prefix
+        self.proj = self.o = None
+
+    def _n(self, short):
+        return self.prefix + short
+
+    def cache_spec(self):
+        return KVCacheSpec(self.num_kv_heads, self.MAPS * self.head_dim, None, v_head_dim=self.v_head_dim)
+
+    def _matrix_specs(self, bias):
+        W, H, G, D, E, M = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.MAPS
+        specs = {self._n("q"): TensorSpec((H * M * D, W)), self._n("k"): TensorSpec((G * M * D, W)), self._n("v"): TensorSpec((G * E, W)),
+                 self._n("o"): TensorSpec((W, H * E))}
+        if bias:
+            specs.update({self._n("q.b"): TensorSpec((H * M * D,), role="bias"), self._n("k.b"): TensorSpec((G * M * D,), role="bias"),
+                          self._n("v.b"): TensorSpec((G * E,), role="bias"), self._n("o.b"): TensorSpec((W,), role="bias")})
+        return specs
+
+    def _bind_matrices(self, tensors, bias):
+        rows = torch.cat([tensors[self._n(m)] for m in "qkv"], dim=0)
+        b = self._vector_f32(torch.cat([tensors[self._n(m + ".b")].float() for m in "qkv"])) if bias else None
+        self.proj = Linear(self._matrix(rows), b, self.rt)              # q, k, v in one product
+        ob = self._vector_f32(tensors[self._n("o.b")].float() * self.out_scale) if bias else None
+        self.o = Linear(self._matrix(tensors[self._n("o")]), ob, self.rt)
+
+
+class DifferentialAttention(_ScoredAttention):
+    MAPS = 2
+
+    def __init__(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, position, diff, eps, v_head_dim=None, scale=None,
+                 out_scale=1.0, prefix="mix."):
+        self._sizes(rt, hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, scale, out_scale, prefix)
+        self.diff, self.eps = float(diff), float(eps)
+        self.position = build_part("position", position, rt)
+        if not hasattr(self.position, "inv_freq"):
+            raise ConfigError("this attention rotates inside its own prepare step and needs a position part with 'inv_freq'")
+        self.lam = None
+
+    def sub_parts(self):
+        return [self.position]
+
+    def tensor_specs(self):
+        specs = self._matrix_specs(bias=False)
+        specs.update({self._n(v): TensorSpec((self.head_dim,), role="lambda_part") for v in ("lq1", "lk1", "lq2", "lk2")})
+        return specs
+
+    def bind(self, tensors):
+        self._bind_matrices(tensors, bias=False)
+        v = {n: tensors[self._n(n)].to(torch.float64) for n in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum())) + self.diff
+
+    def forward(self, x, batch, cache, residual):
+        H, G, D, E = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        g = batch.groups[cache.group]
+        proj = self.proj.forward(x)                                          # fp32 [T, (H+G)*2*D + G*E]
+        freq = self.position.inv_freq
+        q = kernels.scored_prepare(proj, batch.positions, g.slot_mapping if cache.writable else None,
+                                   cache.kv if cache.writable else None, H, G, 2, D, E, cache.page_size, self.rt.dtype,
+                                   inv_freq=freq if freq.numel() else None)
+        o = kernels.scored_attention(q, cache.kv, g, batch, H, G, 2, D, E, cache.page_size, self.scale, lam=self.lam,
+                                     post=1.0 - self.diff, eps=self.eps, out_scale=self.out_scale)
+        self.o.forward(o, accumulate_into=residual)
+
+
+class DistanceBiasAttention(_ScoredAttention):
+    def __init__(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, eps, v_head_dim=None, scale=None, temp_coef=0.0,
+                 temp_every=0.0, out_scale=1.0, prefix="mix."):
+        """``temp_every`` 0: no query temperature."""
+        self._sizes(rt, hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, scale, out_scale, prefix)
+        self.eps, self.temp_coef, self.temp_every = float(eps), float(temp_coef), float(temp_every)
+        self.q_norm = self.k_norm = self.r1 = self.r2 = None
+
+    def tensor_specs(self):
+        H, G, D = self.num_heads, self.num_kv_heads, self.head_dim
+        specs = self._matrix_specs(bias=True)
+        specs.update({self._n("q.norm"): TensorSpec((H * D,), role="norm"), self._n("k.norm"): TensorSpec((G * D,), role="norm"),
+                      self._n("r1"): TensorSpec((H,), role="fraction"), self._n("r2"): TensorSpec((H,), role="fraction")})
+        return specs
+
+    def bind(self, tensors):
+        self._bind_matrices(tensors, bias=True)
+        self.q_norm, self.k_norm = self._vector_f32(tensors[self._n("q.norm")]), self._vector_f32(tensors[self._n("k.norm")])
+        self.r1, self.r2 = self._vector_f32(tensors[self._n("r1")]), self._vector_f32(tensors[self._n("r2")])
+
+    def forward(self, x, batch, cache, residual):
+        H, G, D, E = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        g = batch.groups[cache.group]
+        proj = self.proj.forward(x)                                          # fp32 [T, (H+G)*D + G*E], biases added
+        q = kernels.scored_prepare(proj, batch.positions, g.slot_mapping if cache.writable else None,
+                                   cache.kv if cache.writable else None, H, G, 1, D, E, cache.page_size, self.rt.dtype,
+                                   q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, temp_coef=self.temp_coef,
+                                   temp_every=self.temp_every)
+        o = kernels.scored_attention(q, cache.kv, g, batch, H, G, 1, D, E, cache.page_size, self.scale, r1=self.r1, r2=self.r2,
+                                     out_scale=self.out_scale)
+        self.o.forward(o, accumulate_into=residual)
+
+
+register_part("mixer", "differential_attention", DifferentialAttention, replace=True)
+register_part("mixer", "distance_attention", DistanceBiasAttention, replace=True)
