@@ -90,7 +90,9 @@ def biased_attention(h, w, m, eps):
     k = rms_unit(h @ w["k"].t() + w["k.b"], eps) * w["k.norm"]
     v = (h @ w["v"].t() + w["v.b"]).view(T, G, E)
     p = torch.arange(T, dtype=h.dtype)
-    temp = 1.0 + m["q_temp"]["coef"] * torch.log(torch.floor((p + 1) / m["q_temp"]["every"]) + 1.0)
+    temp = torch.ones(T, dtype=h.dtype)
+    if m.get("q_temp"):                      # a mixer without the key has no temperature
+        temp = 1.0 + m["q_temp"]["coef"] * torch.log(torch.floor((p + 1) / m["q_temp"]["every"]) + 1.0)
     q = (q * temp[:, None]).view(T, H, D)
     k = k.view(T, G, D)
     dist = (p[:, None] - p[None, :]).clamp(min=0)
