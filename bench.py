@@ -162,11 +162,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-shapes", action="store_true", help="skip the Llama-3-8B and Qwen2.5-7B shaped points")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
-    ap.add_argument("--design", default=None, choices=["zatupel"],
+    ap.add_argument("--design", default=None, choices=["zatupel", "tidenex"],
                     help="instead of the default workload: prefill and decode speed of that design at a few layer sizes, "
                          "beside the LLaMA decoder of equal width, depth and head counts")
     a = ap.parse_args()
-    if a.design == "zatupel" and a.impl != "reference":
+    if a.design is not None and a.impl != "reference":
         if a.gpus != 1:
             print(json.dumps({"error": "forge_b200 is a single-GPU engine: bench.py runs at --gpus 1 only", "n_gpus": a.gpus}))
             return 2
@@ -466,8 +466,73 @@ class ZatupelBench(ShapeBench):
         return flops
 
 
+def tidenex_shape(width, layers, heads, kv_heads, dim, ff, state_heads, state_dim, vocab, **_):
+    """A Tidenex configuration at a real model's layer sizes: two layers of differential attention (half as many heads, each
+    with two maps of ``dim`` channels and values of 2*dim, so that the projections are as large as the other decoder's) and one
+    of an attention beside a gated linear recurrence, in turn; no repeated span, so that depth and weights are the other
+    decoder's."""
+    att = {"type": "attention", "mixer": {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": dim, "vdim": 2 * dim, "diff": 0.6,
+                                          "rot": {"dims": dim // 2, "base": 50000.0}, "scale": dim ** -0.5}, "mlp": {"kind": "dense", "ff": ff}}
+    par = {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                                  "q_temp": {"coef": 0.3, "every": 64}},
+                                         "right": {"heads": state_heads, "dim": state_dim, "vdim": state_dim}, "left_scale": 0.8, "right_scale": 1.1},
+           "mlp": {"kind": "dense", "ff": ff}}
+    order = [att, att, par]
+    return {"architecture": "Tidenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 8192,
+            "layers": [order[i % 3] for i in range(layers)]}
+
+
+def tidenex_matmul_params(cfg):
+    """Matrix elements of all layers, and of the head (the embedding table)."""
+    W, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            total += W * (2 * H * D + 2 * G * D + G * E) + W * H * E
+        else:
+            l, r = m["left"], m["right"]
+            H, G, D, E = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+            total += W * (H * D + G * D + G * E) + W * H * E
+            total += W * r["heads"] * (2 * r["dim"] + 2 * r["vdim"])
+        if layer.get("mlp"):
+            total += 2 * W * layer["mlp"]["ff"]
+    return total, cfg.vocab * W
+
+
+class TidenexBench(ShapeBench):
+    """ShapeBench's measurements for a Tidenex configuration: only bytes and FLOPs are counted otherwise."""
+
+    def decode_bytes(self, B, ctx):
+        """Every matrix once, and per request all keys and values and the state matrices, read and written."""
+        cfg = self.cfg
+        layers, head = tidenex_matmul_params(cfg)
+        total = 2 * (layers + head)
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "attention":
+                total += B * ctx * m["kv_heads"] * (2 * m["dim"] + m["vdim"]) * 2
+            else:
+                l, r = m["left"], m["right"]
+                total += B * ctx * l["kv_heads"] * (l["dim"] + l["vdim"]) * 2 + B * 2 * 4 * r["heads"] * r["dim"] * r["vdim"]
+        return total
+
+    def prefill_flops(self, T):
+        cfg = self.cfg
+        layers, head = tidenex_matmul_params(cfg)
+        flops, pairs = 2 * T * layers + 2 * head, T * (T + 1) // 2
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "attention":
+                flops += 2 * pairs * m["heads"] * 2 * (m["dim"] + m["vdim"])
+            else:
+                l, r = m["left"], m["right"]
+                flops += 2 * pairs * l["heads"] * (l["dim"] + l["vdim"]) + 4 * T * r["heads"] * r["dim"] * r["vdim"]
+        return flops
+
+
 def design_arm(a):
-    """Prefill and decode speed of the Zatupel design at a few layer sizes (random weights), each beside the LLaMA decoder
+    """Prefill and decode speed of the Zatupel or Tidenex design at a few layer sizes (random weights), each beside the LLaMA decoder
     of the same width, depth, head counts and feed-forward width run the same way: decode device-timed at batch 1, 8 and
     64 after 512-token prompts, one prompt step of 2,048 tokens.  One JSON line."""
     import torch
@@ -483,7 +548,7 @@ def design_arm(a):
         "w4096": dict(width=4096, layers=4, heads=32, kv_heads=8, dim=128, ff=14336, state_heads=64, state_dim=64, rank=64,
                       window=1024, vocab=32000),
     }
-    out = {"design": "zatupel", "impl": "forge_b200", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": a.warmup,
+    out = {"design": a.design, "impl": "forge_b200", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": a.warmup,
            "data": "synthetic: random-init bf16 weights, uniform-random token ids", "peaks": pk["source"], "sizes": {}}
     clocks = ClockSampler()
     clocks.start()
@@ -492,7 +557,10 @@ def design_arm(a):
                      num_hidden_layers=z["layers"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
                      head_dim=z["dim"], rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=8192)
         row = {}
-        for arch, shape, maker in (("zatupel", zatupel_shape(**z), ZatupelBench), ("llama", llama, ShapeBench)):
+        arms = [("zatupel", zatupel_shape(**z), ZatupelBench), ("llama", llama, ShapeBench)]
+        if a.design == "tidenex":         # beside the hybrid whose kernels are the nearest, and the plain decoder
+            arms.insert(0, ("tidenex", tidenex_shape(**z), TidenexBench))
+        for arch, shape, maker in arms:
             b = maker(shape, PROMPT_LEN, 64, steps, a.warmup, a.block_size, prefill_tokens=PREFILL_TOKENS)
             r = {}
             for B in (1, 8, 64):

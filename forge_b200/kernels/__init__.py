@@ -69,6 +69,8 @@ _SIGNATURES = {
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _I, _P],
         "forge_scored_prepare": [_P, _I] + [_P] * 7 + [_I] * 8 + [_F, _F, _F, _I, _LL, _P],
         "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _P],
+        "forge_scored_mma_supports": [_I] * 6,
+        "forge_scored_attention_mma": [_P] * 11 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
@@ -89,7 +91,7 @@ _libs = {}
 # library the bounds, per library (one per source file that checks):
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
                   "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma",
-                             "forge_checks_configure_attention_scored"],
+                             "forge_checks_configure_attention_scored", "forge_checks_configure_attention_scored_mma"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -880,6 +882,20 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
     q's type, times ``out_scale``."""
     lib = library("mixers")
     T = q.shape[0]
+    if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_scored_mma_supports.fn(H, G, M, D, E, page_size):
+        # tensor cores: every (head, map) a one-pass attention of its own; two maps meet in a second small kernel
+        t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
+        u = new_tensor((T, H, M, E), torch.float32, q.device) if M == 2 else None
+        out = new_tensor((T, H * E), q.dtype, q.device)
+        _check(lib, lib.forge_scored_attention_mma(
+            _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
+            _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+            _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _opt(u, "u", torch.float32),
+            _need(out, "out", torch.bfloat16), T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
+            float(scale), float(lam), float(post), float(eps), float(out_scale), _stream()), "scored_attention_mma")
+        if M == 2:
+            count_launches(1)      # the kernel that combines the two maps
+        return out
     single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
     TQ = scored_tile_tokens(H, G, M, D, E, single_tokens=single)
     t0, tn, tiles = headmix_plan(batch, TQ, q.device)

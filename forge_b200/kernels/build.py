@@ -31,7 +31,7 @@ LIBRARIES = {
     "attention_sm100": ["attention_sm100.cu"],
     # attention whose heads exchange weights, over a window with kept first tokens; attention with shaped scores (two maps per
     # head, a distance term); mixers with a matrix of state per head
-    "mixers": ["attention_headmix.cu", "attention_headmix_mma.cu", "attention_scored.cu", "recurrent.cu"],
+    "mixers": ["attention_headmix.cu", "attention_headmix_mma.cu", "attention_scored.cu", "attention_scored_mma.cu", "recurrent.cu"],
     # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)
     "decode_layers": ["decode_layers.cu"],
 }
