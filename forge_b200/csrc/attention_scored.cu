@@ -23,7 +23,8 @@ namespace {
 
 constexpr int kPrepThreads = 256;
 
-// One CTA per token.  proj fp32 row = [q: QU units of D | k: KU units of D | v: G heads of E].
+// One CTA per token, or (steps of few tokens) several that share a token's channels; each of them takes the norms' sums over
+// the whole row, which is cheaper than a second launch.  proj fp32 row = [q: QU units of D | k: KU units of D | v: G heads of E].
 template <typename TC>
 __global__ void __launch_bounds__(kPrepThreads)
 scored_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __restrict__ positions,
@@ -63,7 +64,8 @@ scored_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __r
         else if (k_norm) x = x * inv_k * k_norm[idx - QW];
         return x;
     };
-    for (int idx = threadIdx.x; idx < QW + KW; idx += kPrepThreads) {
+    const int first = blockIdx.y * kPrepThreads + threadIdx.x, step = gridDim.y * kPrepThreads;
+    for (int idx = first; idx < QW + KW; idx += step) {
         const int d = idx % D;
         float x = value(idx);
         if (d < rot_dims) {
@@ -79,7 +81,7 @@ scored_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __r
         }
     }
     if (store)
-        for (int idx = threadIdx.x; idx < G * E; idx += kPrepThreads)
+        for (int idx = first; idx < G * E; idx += step)
             vbase[((size_t)(idx / E) * page_size + off) * E + idx % E] = forge::from_float<TC>(row[QW + KW + idx]);
 }
 
@@ -249,7 +251,7 @@ extern "C" int forge_scored_prepare(const float* proj, int ld, const int32_t* po
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(scored_prepare_kernel<TT>, dim3(T), dim3(kPrepThreads), 0, stream, 1, proj, ld, positions, slot_mapping,
+        e = forge::launch(scored_prepare_kernel<TT>, dim3(T, T >= 256 ? 1 : min(16, ((QU + KU) * D + 511) / 512)), dim3(kPrepThreads), 0, stream, 1, proj, ld, positions, slot_mapping,
                           inv_freq, q_norm, k_norm, (TT*)q_out, (TT*)cache, QU, KU, G, D, E, rot_dims, eps, temp_coef, temp_every,
                           page_size, page_stride));
     return forge::check_launch("scored_prepare", e);

@@ -7,7 +7,7 @@
 // of VC value columns, and walks the keys in tiles of 64 positions that start at multiples of 64.  With one map the result
 // goes out in bfloat16 at once; with two, each map leaves its normalised output in fp32 and a second kernel takes
 // a_1 - lambda a_2, divides by the root mean square and scales.  The distance term is taken off the scores in fp32 before
-// the softmax.  mma.sync m16n8k16 (the legacy tensor path): S = Q K^T with K rows as the column-major operand, O += P V with
+// the softmax (with the fast base-2 logarithm; the 32-bit kernel of attention_scored.cu uses log1pf).  mma.sync m16n8k16 (the legacy tensor path): S = Q K^T with K rows as the column-major operand, O += P V with
 // V through ldmatrix.trans; the softmax weights are rounded to bfloat16 as the value product's operand, their sums are not.
 #include "common.cuh"
 #include "checks.cuh"
@@ -48,18 +48,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// M == 1: out bf16 [T, H, E] (times out_scale).  M == 2: u fp32 [T, H, M, E], normalised.
+// M == 1 and nsplit == 1: out bf16 [T, H, E] (times out_scale).  Otherwise u fp32 [nsplit, T, H, M, E]: normalised with
+// nsplit == 1; with nsplit > 1 (steps of single tokens: a request's key tiles are dealt out to nsplit CTAs in runs) each run
+// leaves its sums as they are, beside the row's maximum (in units of log2 e) and sum in part_ml [nsplit, T, H, M, 2].
 template <int VC>
 __global__ void __launch_bounds__(kThreads)
 scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ u,
-                  __nv_bfloat16* __restrict__ out, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
+                  __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
                   int max_pages, float scale, float out_scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
-    const int tile = blockIdx.x, c = blockIdx.y / M, mp = blockIdx.y % M, v0 = blockIdx.z * VC;
+    // the last tiles of a prompt see the most keys: they start first, so that the short ones fill the grid's tail
+    const int tile = gridDim.x / nsplit - 1 - blockIdx.x / nsplit, sp = blockIdx.x % nsplit, c = blockIdx.y / M, mp = blockIdx.y % M, v0 = blockIdx.z * VC;
     const int t0 = tile_t0 ? tile_t0[tile] : tile;
     const int nq = tile_n ? tile_n[tile] : 1;
     if (!FORGE_TOKEN_OK(t0) || !FORGE_TOKEN_OK(t0 + nq - 1)) return;
@@ -132,15 +135,16 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         }
         copies_commit();
     };
-    fetch(0, 0);
-    for (int kt = 0; kt <= last_tile; ++kt) {
+    const int n_tiles = last_tile + 1, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = sp * per, kt_hi = min(n_tiles, kt_lo + per);
+    if (kt_lo < kt_hi) fetch(kt_lo, 0);
+    for (int kt = kt_lo; kt < kt_hi; ++kt) {
         const int j0 = kt * BN;
-        if (kt + 1 <= last_tile) fetch(kt + 1, (kt + 1) & 1);
+        if (kt + 1 < kt_hi) fetch(kt + 1, (kt + 1 - kt_lo) & 1);
         else copies_commit();
         copies_wait<1>();
         __syncthreads();                                                  // tile kt has landed for every thread
-        const __nv_bfloat16* Kt = Ks + (kt & 1) * stage;
-        const __nv_bfloat16* Vt = Vs + (kt & 1) * stage;
+        const __nv_bfloat16* Kt = Ks + ((kt - kt_lo) & 1) * stage;
+        const __nv_bfloat16* Vt = Vs + ((kt - kt_lo) & 1) * stage;
 
         // a warp whose 16 rows lie beyond the tile's rows (a single token brings H/G rows) has nothing to compute
         if (rb * 16 < rows) {
@@ -183,7 +187,9 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                         float s = -INFINITY;
                         if (ok) {
                             s = sacc[nt][e] * sl2;
-                            if (r1) s -= kLog2e * r1v[hi] * log1pf(r2v[hi] * (float)(pos - j));
+                            // r1 ln(1 + r2 d) in units of log2(e) is r1 log2(1 + r2 d); lg2.approx errs by 2^-22, far below
+                            // the rounding of the bfloat16 operands of q . k
+                            if (r1) s -= r1v[hi] * __log2f(fmaf(r2v[hi], (float)(pos - j), 1.0f));
                         }
                         sacc[nt][e] = s;
                         tmax[hi] = fmaxf(tmax[hi], s);
@@ -240,42 +246,72 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         }
         __syncthreads();                                                  // before a later fetch writes into this buffer
     }
-    const float inv[2] = {row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f, row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f};
+    const float inv[2] = {nsplit > 1 ? 1.0f : (row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f), nsplit > 1 ? 1.0f : (row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f)};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = h ? r_hi : r_lo;
         if (r >= rows || rb * 16 >= rows) continue;
-        const size_t head_index = (size_t)(t0 + r / Gq) * H + c * Gq + r % Gq;
+        const size_t head_index = (size_t)sp * T * H + (size_t)(t0 + r / Gq) * H + c * Gq + r % Gq;
+        if (nsplit > 1 && blockIdx.z == 0 && (lane & 3) == 0 && (!colsplit || warp == 0)) {
+            part_ml[(head_index * M + mp) * 2] = row_m[h];
+            part_ml[(head_index * M + mp) * 2 + 1] = row_l[h];
+        }
 #pragma unroll
         for (int nt = 0; nt < VC / 8; ++nt) {
             if (nt >= ntw) break;
             const int col = v0 + cb + nt * 8 + (lane & 3) * 2;
             if (col >= E) continue;
             const float a = oacc[nt][2 * h] * inv[h], b = oacc[nt][2 * h + 1] * inv[h];
-            if (M == 1) *reinterpret_cast<uint32_t*>(out + head_index * E + col) = pack_bf16(a * out_scale, b * out_scale);
+            if (M == 1 && nsplit == 1) *reinterpret_cast<uint32_t*>(out + head_index * E + col) = pack_bf16(a * out_scale, b * out_scale);
             else *reinterpret_cast<float2*>(u + (head_index * M + mp) * E + col) = make_float2(a, b);
         }
     }
 }
 
-// Two maps: a warp per (token, head) takes o = a_1 - lambda a_2 from u fp32 [T, H, 2, E], divides it by its root mean square
-// (eps inside the root) and multiplies by post; out bf16 [T, H, E].
+// A warp per (token, head): puts the runs of key tiles together (nsplit > 1: run s of a map counts with
+// 2^(m_s - m) / sum_s 2^(m_s - m) l_s), and with two maps takes o = a_1 - lambda a_2 from u fp32 [nsplit, T, H, M, E], divides it
+// by its root mean square (eps inside the root) and multiplies by post; with one map the output is the map's, times post.
+// out bf16 [T, H, E].
 __global__ void __launch_bounds__(128)
-scored_combine_kernel(const float* __restrict__ u, __nv_bfloat16* __restrict__ out, int rows, int E, float lambda, float post, float eps) {
+scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, __nv_bfloat16* __restrict__ out, int rows,
+                      int M, int E, float lambda, float post, float eps) {
+    constexpr int kMaxSplit = 16;
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows) return;
-    const float* a1 = u + (size_t)w * 2 * E;
-    const float* a2 = a1 + E;
+    float wt[2][kMaxSplit];              // the weight of run s of map m (nsplit == 1: one)
+    for (int m = 0; m < M; ++m) {
+        if (nsplit == 1) { wt[m][0] = 1.0f; continue; }
+        float mx = -INFINITY, den = 0.f;
+        for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, part_ml[(((size_t)s * rows + w) * M + m) * 2]);
+        for (int s = 0; s < nsplit; ++s) {
+            const size_t at = (((size_t)s * rows + w) * M + m) * 2;
+            const float l = part_ml[at + 1];
+            const float x = l > 0.f ? exp2f(part_ml[at] - mx) : 0.f;          // a run that saw no key counts for nothing
+            wt[m][s] = x;
+            den = fmaf(x, l, den);
+        }
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        for (int s = 0; s < nsplit; ++s) wt[m][s] *= inv;
+    }
+    auto value = [&](int m, int e) {
+        float a = 0.f;
+        for (int s = 0; s < nsplit; ++s) a = fmaf(wt[m][s], u[(((size_t)s * rows + w) * M + m) * E + e], a);
+        return a;
+    };
+    if (M == 1) {
+        for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn(value(0, e) * post);
+        return;
+    }
     float ss = 0.f;
     for (int e = lane; e < E; e += 32) {
-        const float o = a1[e] - lambda * a2[e];
+        const float o = value(0, e) - lambda * value(1, e);
         ss = fmaf(o, o, ss);
     }
     ss = forge::warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)E + eps) * post;
-    for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn((a1[e] - lambda * a2[e]) * inv);
+    for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn((value(0, e) - lambda * value(1, e)) * inv);
 }
 
 forge::PerDeviceFlag g_attr_done[3];
@@ -283,8 +319,8 @@ forge::PerDeviceFlag g_attr_done[3];
 template <int VC>
 int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                   const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, const float* r1,
-                  const float* r2, float* u, __nv_bfloat16* out, int qrows, int H, int G, int M, int D, int E, int page_size,
-                  long long page_stride, int max_pages, float scale, float out_scale) {
+                  const float* r2, float* u, __nv_bfloat16* out, float* part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E,
+                  int page_size, long long page_stride, int max_pages, float scale, float out_scale) {
     bool& done = g_attr_done[which].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(scored_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
@@ -293,7 +329,8 @@ int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const 
     }
     return forge::check_launch("scored_attention_mma",
                                forge::launch(scored_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
-                                             tn, r1, r2, u, out, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, out_scale));
+                                             tn, r1, r2, u, out, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale,
+                                             out_scale));
 }
 
 }  // namespace
@@ -305,18 +342,21 @@ extern "C" int forge_scored_mma_supports(int H, int G, int M, int D, int E, int 
             D % 16 == 0 && D >= 16 && D <= 128 && E % 8 == 0 && E > 0) ? 1 : 0;
 }
 
-// q bf16 [T, H*M*D]; u fp32 [T, H, M, E] (scratch, M == 2 only); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive
+// q bf16 [T, H*M*D]; u fp32 [nsplit, T, H, M, E] (scratch; not needed with M == 1 and nsplit == 1); part_ml fp32
+// [nsplit, T, H, M, 2] (scratch, nsplit > 1: steps of single tokens only); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive
 // tokens of one request with tile_n * (H/G) <= 64 (both null: one token per tile, num_tiles = T).  r1, r2 fp32 [H] or null.
 extern "C" int forge_scored_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* r1,
-                                          const float* r2, float* u, void* out, int T, int num_tiles, int H, int G, int M, int D, int E,
+                                          const float* r2, float* u, float* part_ml, int nsplit, void* out, int T, int num_tiles, int H, int G, int M, int D, int E,
                                           int page_size, long long page_stride, int max_pages, float scale, float lambda, float post,
                                           float eps, float out_scale, cudaStream_t stream) {
     if (!forge_scored_mma_supports(H, G, M, D, E, page_size))
         return forge::fail(FORGE_ERR_UNSUPPORTED, "scored_attention_mma: H=%d G=%d M=%d D=%d E=%d", H, G, M, D, E);
     if (T < 0 || num_tiles < 0 || max_pages <= 0 || (tile_t0 == nullptr) != (tile_n == nullptr) || (r1 == nullptr) != (r2 == nullptr) ||
-        (M == 2 && !u))
+        ((M == 2 || nsplit > 1) && !u))
         return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: bad arguments");
+    if (nsplit < 1 || nsplit > 16 || (nsplit > 1 && (tile_t0 != nullptr || part_ml == nullptr)))
+        return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: the keys are dealt out to several CTAs only in steps of single tokens");
     if (T == 0 || num_tiles == 0) return FORGE_OK;
     int VC = 64;                        // the chunk width that wastes the fewest columns; among equals the widest
     for (int cand : {128, 256})
@@ -325,19 +365,20 @@ extern "C" int forge_scored_attention_mma(const void* q, const void* cache, cons
     // a step of single tokens brings H/G rows a tile: 16 rows of queries in shared memory leave room for more CTAs on the SM
     const int qrows = (tile_t0 == nullptr && H / G <= 16) ? 16 : BM;
     const size_t smem = sizeof(__nv_bfloat16) * ((size_t)qrows * (D + kPad) + 2 * (size_t)BN * ((D + kPad) + (VC + kPad)));
-    const dim3 grid(num_tiles, G * M, chunks);
+    const dim3 grid(num_tiles * nsplit, G * M, chunks);
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
-    const float os = M == 1 ? out_scale : 1.0f;
+    const float os = (M == 1 && nsplit == 1) ? out_scale : 1.0f;
     int rc;
-    if (VC == 64) rc = launch_scored<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
-    else if (VC == 128) rc = launch_scored<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
-    else rc = launch_scored<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
-    if (rc != FORGE_OK || M == 1) return rc;
+    if (VC == 64) rc = launch_scored<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
+    else if (VC == 128) rc = launch_scored<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
+    else rc = launch_scored<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
+    if (rc != FORGE_OK || (M == 1 && nsplit == 1)) return rc;
     const unsigned blocks = (unsigned)(((size_t)T * H + 3) / 4);
-    return forge::check_launch("scored_combine", forge::launch(scored_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, (const float*)u, ob,
-                                                               T * H, E, lambda, post * out_scale, eps));
+    return forge::check_launch("scored_combine", forge::launch(scored_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, (const float*)u,
+                                                               (const float*)part_ml, nsplit, ob, T * H, M, E, lambda,
+                                                               (M == 1 ? 1.0f : post) * out_scale, eps));
 }
 
 FORGE_DEFINE_CHECKS_ENTRY(attention_scored_mma)

@@ -68,6 +68,17 @@ template <int BN> struct Cfg {
 #ifndef FORGE_GATE_GELU
 #define FORGE_GATE_GELU 0
 #endif
+// The activation of the epilogue that stores bfloat16 (EPI_STORE_BF16): none in the ordinary build; in a library built with
+// -DFORGE_CAST_ACT=1 the exact gelu, v/2 (1 + erf(v / sqrt 2)), the activation between the two products of an ungated
+// feed-forward.  A variant of its own for the same reason as the gelu gate: the ordinary build's epilogues stay as they were.
+#ifndef FORGE_CAST_ACT
+#define FORGE_CAST_ACT 0
+#endif
+#if FORGE_CAST_ACT == 1
+#define FORGE_CAST(v) (0.5f * (v) * (1.0f + erff((v) * 0.7071067811865476f)))
+#else
+#define FORGE_CAST(v) (v)
+#endif
 __device__ __forceinline__ bool is_gated(int epilogue) { return epilogue == EPI_SWIGLU_BF16 || epilogue == EPI_GEGLU_BF16; }
 __device__ __forceinline__ float gate_act(int epilogue, float g) {
 #if FORGE_GATE_GELU
@@ -112,8 +123,8 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
             if (width == 32 && (p.N & 7) == 0) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(FORGE_CAST(v[i]), FORGE_CAST(v[i + 1])), h1 = __floats2bfloat162_rn(FORGE_CAST(v[i + 2]), FORGE_CAST(v[i + 3]));
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(FORGE_CAST(v[i + 4]), FORGE_CAST(v[i + 5])), h3 = __floats2bfloat162_rn(FORGE_CAST(v[i + 6]), FORGE_CAST(v[i + 7]));
                     uint4 o;
                     o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
                     o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
@@ -121,7 +132,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(v[i]);
+                for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(FORGE_CAST(v[i]));
             }
         } else {   // EPI_SWIGLU_BF16, EPI_GEGLU_BF16: N is even, pairs never straddle a 32-column chunk
             const int half_n = p.N >> 1;
@@ -1127,7 +1138,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                                     __float2bfloat16_rn(gate_act(p.epilogue, v) * other);
                         } else if (n < p.N) {
                             if (p.epilogue == EPI_STORE_BF16) {
-                                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(FORGE_CAST(v));
                             } else {
                                 // the residual add is a reduction that the L2 performs: nothing is read back, so
                                 // the kernel's last step is a store either way (one add per element: the order
@@ -1184,7 +1195,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             } else if (p.epilogue == EPI_STORE_BF16) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) if (n + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+                for (int i = 0; i < 4; ++i) if (n + i < p.N) dst[i] = __float2bfloat16_rn(FORGE_CAST(v[i]));
             } else {
                 float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
                 const bool accum = p.epilogue == EPI_ACCUM_F32;
@@ -1403,7 +1414,7 @@ gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                             __float2bfloat16_rn(gate_act(p.epilogue, v) * other);
                 } else if (n < p.N) {
                     if (p.epilogue == EPI_STORE_BF16) {
-                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(FORGE_CAST(v));
                     } else {
                         float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
                         *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;

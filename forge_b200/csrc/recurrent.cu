@@ -101,7 +101,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
                   const int32_t* __restrict__ slots, float* __restrict__ out, const TA* __restrict__ last_in, int W,
                   long long prev_off, int N, int K, int KV, int vec) {
     constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
-    __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
+    __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][MODE == 2 ? 1 : kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
     __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
     __shared__ float is[2][kScanTokens];                                // MODE 1: 1 / (|k|^2 + 1e-6) of the staged tokens
     forge::pdl_launch_dependents();
@@ -112,7 +112,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
     // channels beyond K stay zero in every staged vector: the copies never touch them
     for (int i = tid; i < 2 * kScanTokens * KMAX; i += kScanThreads) {
         (&rs[0][0][0])[i] = 0.f;
-        if (MODE != 2) (&ks[0][0][0])[i] = 0.f;
+        if (MODE != 2) (&ks[0][0][0])[i] = 0.f;          // (mode 2 has no keys: its ks is a stub that nothing reads)
         (&ds[0][0][0])[i] = 0.f;
         if (MODE == 1) (&as[0][0][0])[i] = 0.f;
     }
@@ -308,6 +308,12 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
     case KM:                                                                                                                 \
         return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, inv, state, \
                              stride, q_start, slots, out, last_in, W, prev_off, N, K, KV, vec);
+    if constexpr (MODE == 2) {            // the gated write stages no keys: heads of up to 256 key channels fit its shared memory
+        switch (kmax) {
+            FORGE_SCAN_CASE(192) FORGE_SCAN_CASE(256)
+            default: break;
+        }
+    }
     switch (kmax) {
         FORGE_SCAN_CASE(32) FORGE_SCAN_CASE(64) FORGE_SCAN_CASE(96) FORGE_SCAN_CASE(128)
         default: return cudaErrorInvalidValue;
@@ -331,13 +337,13 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
                                 int T, int S, int N, int K, int KV, cudaStream_t stream) {
     if (T < 0 || S < 0 || N <= 0 || K <= 0 || KV <= 0 || mode < 0 || mode > 2 || (mode != 2 && KV != K))
         return forge::fail(FORGE_ERR_ARG, "state_scan: bad sizes S=%d N=%d K=%d mode=%d", S, N, K, mode);
-    if (K > 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "state_scan: heads of %d channels (at most 128)", K);
+    if (K > (mode == 2 ? 256 : 128)) return forge::fail(FORGE_ERR_UNSUPPORTED, "state_scan: heads of %d channels (at most %d)", K, mode == 2 ? 256 : 128);
     if (state_stride < (long long)N * K * KV) return forge::fail(FORGE_ERR_ARG, "state_scan: state rows are too short");
     if (mode == 0 && !bonus) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 0 needs the bonus");
     if (mode == 1 && (!y || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 1 needs the removal rate");
     if (mode == 2 && (y != r || ld_y != ld_r || !a0)) return forge::fail(FORGE_ERR_ARG, "state_scan: mode 2 takes y = r and the gate's lower bound");
     if (S == 0) return FORGE_OK;
-    const int kmax = (K + 31) / 32 * 32;
+    const int kmax = K <= 128 ? (K + 31) / 32 * 32 : (K <= 192 ? 192 : 256);
     const dim3 grid(S, N, (KV + kCols - 1) / kCols);
     // decays (and removal rates, and the unit keys' divisors) for all tokens at once, in place
     {

@@ -70,7 +70,7 @@ _SIGNATURES = {
         "forge_scored_prepare": [_P, _I] + [_P] * 7 + [_I] * 8 + [_F, _F, _F, _I, _LL, _P],
         "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _P],
         "forge_scored_mma_supports": [_I] * 6,
-        "forge_scored_attention_mma": [_P] * 11 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_P],
+        "forge_scored_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
@@ -885,16 +885,23 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
     if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_scored_mma_supports.fn(H, G, M, D, E, page_size):
         # tensor cores: every (head, map) a one-pass attention of its own; two maps meet in a second small kernel
         t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
-        u = new_tensor((T, H, M, E), torch.float32, q.device) if M == 2 else None
+        nsplit = 1
+        if getattr(batch, "decode_only", False):
+            # a step of single tokens brings T * G * M * (value chunks) CTAs: deal a request's key tiles out to several, up to one
+            # CTA per SM, as far as the longest context (the graph's bucket) has tiles
+            ctas = T * G * M * -(-E // 256)
+            nsplit = max(1, min(8, -(-batch.max_context // 64), _sm_count(q.device) // max(1, ctas)))
+        u = new_tensor((nsplit, T, H, M, E), torch.float32, q.device) if (M == 2 or nsplit > 1) else None
+        part_ml = new_tensor((nsplit, T, H, M, 2), torch.float32, q.device) if nsplit > 1 else None
         out = new_tensor((T, H * E), q.dtype, q.device)
         _check(lib, lib.forge_scored_attention_mma(
             _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
             _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
             _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _opt(u, "u", torch.float32),
-            _need(out, "out", torch.bfloat16), T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
+            _opt(part_ml, "part_ml", torch.float32), nsplit, _need(out, "out", torch.bfloat16), T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
             float(scale), float(lam), float(post), float(eps), float(out_scale), _stream()), "scored_attention_mma")
-        if M == 2:
-            count_launches(1)      # the kernel that combines the two maps
+        if M == 2 or nsplit > 1:
+            count_launches(1)      # the kernel that puts the runs of key tiles, and the two maps, together
         return out
     single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
     TQ = scored_tile_tokens(H, G, M, D, E, single_tokens=single)
@@ -1349,14 +1356,16 @@ def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_d
 
 EPILOGUES = {"none": 0, "accumulate": 1, "cast": 2, "swiglu": 3, "geglu": 5}
 GELU_GATE_VARIANT = {"FORGE_GATE_GELU": 1}
+GELU_CAST_VARIANT = {"FORGE_CAST_ACT": 1}        # the library whose bfloat16 store applies the exact gelu first
 
 
 def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None):
     """bf16 x [M,K] . w [N,K]^T on the tcgen05 tensor cores, fp32 accumulation.
     epilogue "none": fp32 [M,N] (added into ``accumulate_into`` when given); "cast": bf16 [M,N];
-    "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]; "geglu": the same with the tanh form of gelu."""
+    "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]; "geglu": the same with the tanh form of gelu; "gelu": bf16 [M,N] =
+    y/2 (1 + erf(y / sqrt 2))."""
     # the gelu gate lives in a variant of the library of its own, so that the silu epilogues stay as short as they were
-    lib = library("gemm_sm100", GELU_GATE_VARIANT) if epilogue == "geglu" else library("gemm_sm100")
+    lib = library("gemm_sm100", GELU_GATE_VARIANT if epilogue == "geglu" else GELU_CAST_VARIANT if epilogue == "gelu" else None)
     (M, K), (N, K2) = x.shape, w.shape
     if K != K2:
         raise KernelError(f"gemm_sm100: x {tuple(x.shape)} does not match w {tuple(w.shape)}")
@@ -1367,7 +1376,7 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
             out = new_tensor((M, N), torch.float32, x.device) if out is None else out
             code = EPILOGUES["none"]
         want_shape, want_dtype = (M, N), torch.float32
-    elif epilogue == "cast":
+    elif epilogue in ("cast", "gelu"):
         out = new_tensor((M, N), torch.bfloat16, x.device) if out is None else out
         code, want_shape, want_dtype = EPILOGUES["cast"], (M, N), torch.bfloat16
     elif epilogue in ("swiglu", "geglu"):

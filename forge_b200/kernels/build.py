@@ -149,4 +149,5 @@ def build_all(force=False):
         else:
             out[name] = build_library(name, force=force)
     out["gemm_sm100_gate_gelu1"] = build_library("gemm_sm100", force=force, defines={"FORGE_GATE_GELU": 1})
+    out["gemm_sm100_cast_act1"] = build_library("gemm_sm100", force=force, defines={"FORGE_CAST_ACT": 1})
     return out

@@ -31,6 +31,8 @@ class Linear:
         epilogue "cast":   rt.dtype [M,N]
         epilogue "gelu" | "gelu_tanh" | "silu":  rt.dtype [M,N], the activation of every element
         """
+        if epilogue == "gelu" and self.tensor_core:
+            return kernels.gemm_sm100(x, self.weight, bias=self.bias, epilogue="gelu")      # the activation in the product's epilogue
         if epilogue in kernels.ACTIVATIONS:
             y = kernels.gemm_sm100(x, self.weight, bias=self.bias) if self.tensor_core else kernels.gemm_simt(x, self.weight, bias=self.bias)
             return kernels.act_rows(y, self.rt.dtype, epilogue)

@@ -131,8 +131,8 @@ class GatedWriteMixer(Part):
     graph_safe = True       # request boundaries and state rows come from the batch's device tensors (q_start, slots)
 
     def __init__(self, rt, hidden_size, num_heads, head_dim, eps, v_head_dim=None, out_scale=1.0, prefix="mix."):
-        if head_dim > 128:
-            raise ConfigError(f"state mixers take heads of up to 128 key channels, not {head_dim}")
+        if head_dim > 256:
+            raise ConfigError(f"the gated-write mixer takes heads of up to 256 key channels, not {head_dim}")
         self.rt, self.hidden_size, self.num_heads, self.head_dim = rt, hidden_size, num_heads, head_dim
         self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
         self.eps, self.out_scale, self.prefix = float(eps), float(out_scale), prefix

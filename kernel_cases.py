@@ -142,7 +142,53 @@ def case(name):
             else:
                 state_scan("decay_bonus", (r, 0), (k, 0), (v, 0), (x, 0), w0, state, batch, N, K, bonus=u)
         return run, 4 * T * N * K * 4, (8 if name.endswith("delta") else 6) * T * N * K * K
-    raise SystemExit(f"unknown case {name!r}; known: headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
+    if name in ("scored_attention_prefill", "scored_attention_decode", "distance_attention_prefill"):
+        # attention with shaped scores: differential (16 / 4 kv heads, two maps of 64 channels, values of 128) or with the
+        # distance term (32 / 4 kv heads of 64); pages of 64; one request of 2,048 tokens, or 8 requests of one token on 1,023
+        from forge_b200.kernels import scored_attention
+        ps = 64
+        Hh, G, M, D, E = (32, 4, 1, 64, 64) if name.startswith("distance") else (16, 4, 2, 64, 128)
+        reqs = [(1023, 1)] * 8 if name.endswith("decode") else [(0, 2048)]
+        pages_per = [-(-(c + n) // ps) for c, n in reqs]
+        table = torch.full((len(reqs), max(pages_per)), -1, dtype=torch.int32)
+        q_start, nxt = [0], 0
+        for s_, n in enumerate(pages_per):
+            table[s_, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+            nxt += n
+            q_start.append(q_start[-1] + reqs[s_][1])
+        T = q_start[-1]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(num_requests=len(reqs), num_tokens=T, host_q_start=q_start, attention_plan={},
+                                tok_req=i32([s_ for s_, (c, n) in enumerate(reqs) for _ in range(n)]),
+                                positions=i32([c + j for c, n in reqs for j in range(n)]))
+        if name.endswith("decode"):
+            batch.decode_only, batch.max_context = True, 1024
+        g = SimpleNamespace(block_table=table.to(DEV))
+        q, cache = _bf16(T, Hh * M * D), _bf16(nxt, G * ps * (M * D + E))
+        r1 = torch.rand(Hh, device=DEV) if M == 1 else None
+        r2 = torch.rand(Hh, device=DEV) if M == 1 else None
+        pairs = sum(c + j + 1 for c, n in reqs for j in range(n))
+        return (lambda: scored_attention(q, cache, g, batch, Hh, G, M, D, E, ps, D ** -0.5, r1=r1, r2=r2, lam=0.7, post=0.4, eps=1e-5)), \
+            pairs * G * (M * D + E) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * M * (D + E)
+    if name == "state_scan_gated":
+        # the gated-write recurrence alone: one request of 1,024 tokens, 32 heads of 64 key and 64 value channels (4 FLOPs per
+        # state element and token), with the kernel that makes the gates in front of it
+        from forge_b200.kernels import state_scan
+        T, N, K = 1024, 32, 64
+        mk = lambda: torch.randn(T, N * K, device=DEV) * 0.5
+        r, v, x = mk(), mk(), mk()
+        r0, x0 = r.clone(), x.clone()
+        fb, low = torch.randn(N * K, device=DEV), torch.rand(N * K, device=DEV)
+        state = torch.zeros(2, N * K * K, device=DEV)
+        i32 = lambda z: torch.tensor(z, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(q_start=i32([0, T]), slots=i32([1]), num_requests=1)
+
+        def run():
+            r.copy_(r0)             # the scan overwrites r with silu(r) and x with the gates
+            x.copy_(x0)
+            state_scan("gated_write", (r, 0), None, (v, 0), (x, 0), fb, state, batch, N, K, a0=low, KV=K)
+        return run, 3 * T * N * K * 4, 4 * T * N * K * K
+    raise SystemExit(f"unknown case {name!r}; known: scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
                      "gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "

@@ -125,7 +125,7 @@ def test_distance_attention_alone(dtype, kind):
         assert max_rel_err(got[r], want) <= PART_TOL[dtype], (kind, r)
 
 
-GATED = [(3, 10, 6), (2, 6, 10), (5, 12, 20), (1, 40, 24), (4, 64, 32), (2, 32, 64), (2, 128, 16), (1, 8, 130)]
+GATED = [(3, 10, 6), (2, 6, 10), (5, 12, 20), (1, 40, 24), (4, 64, 32), (2, 32, 64), (2, 128, 16), (1, 8, 130), (1, 160, 8), (2, 256, 24)]
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -219,7 +219,8 @@ def test_side_by_side_mixers_in_a_layer(dtype):
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("page_size", [8, 64])
 @pytest.mark.parametrize("maps", [1, 2])
-def test_one_key_that_stands_out(dtype, page_size, maps):
+@pytest.mark.parametrize("D, E", [(8, 2), (16, 8)])          # the second pair is one that the tensor-core kernel takes in bfloat16
+def test_one_key_that_stands_out(dtype, page_size, maps, D, E):
     """Keys are zero except one whose score is huge for head 0's first map; values carry their position.  That map returns the
     key's position if the token sees it (far back among hundreds, at a page's border, the token itself) and the mean of the
     visible positions if it does not (the key lies ahead, in the same portion); every other map returns the mean.  With two
@@ -228,7 +229,7 @@ def test_one_key_that_stands_out(dtype, page_size, maps):
     from forge_b200.cache import CacheStorage
     from forge_b200.engine import StepEntry, build_step_batch
     from forge_b200.parts import KVCacheSpec
-    H, G, D, E, N, P = 2, 1, 8, 2, 300, 27
+    H, G, N, P = 2, 1, 300, 27
     lam, post, eps = 0.4, 0.7, 1e-6
     dev = torch.device(DEV)
     storage = CacheStorage([KVCacheSpec(G, maps * D, None, v_head_dim=E)], [None], page_size, 64 * 8 // page_size, 2, dtype, dev)
@@ -261,7 +262,7 @@ def test_one_key_that_stands_out(dtype, page_size, maps):
                         want = [first, 1.0]
                     else:
                         o = [first - lam * mean, 1.0 - lam]
-                        rms = math.sqrt((o[0] ** 2 + o[1] ** 2) / 2 + eps)
+                        rms = math.sqrt((o[0] ** 2 + o[1] ** 2) / E + eps)          # the other value channels are zero
                         want = [o[0] / rms * post, o[1] / rms * post]
                     scale = max(1.0, abs(want[0]))
                     assert abs(out[t, h, 0] - want[0]) <= tol * scale and abs(out[t, h, 1] - want[1]) <= tol * scale, \
@@ -474,3 +475,19 @@ def test_trace_replay_as_a_subprocess(tid, tmp_path):
         ref = torch.stack([want[rid][pos] for rid, pos in rows])
         assert max_rel_err(got, ref) <= TOL["float32"], n
     assert sorted(os.listdir(out)) == sorted(f"{n}.f32" for n in asked)
+
+
+def test_command_line(tid):
+    """bin/forge-cli on a Tidenex folder: greedy tokens in 32-bit follow the plain implementation; sampling runs."""
+    name, d, plain, reqs, want = tid
+    prompt = reqs["r1"][:6]
+    cli = [sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p", " ".join(map(str, prompt)), "-n", "5", "--no-stream",
+           "--page-size", "8", "--kv-pages", "2"]
+    proc = subprocess.run(cli + ["--temp", "0", "--repeat-penalty", "1.0", "--dtype", "float32"], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [int(t) for t in proc.stdout.strip().splitlines()[0].split()]
+    assert len(got) == 5 and "6 prompt" in proc.stdout and "5 generated" in proc.stdout
+    assert_greedy_follows_plain(lambda ids: plain.forward(ids).float(), prompt, got, TOL["float32"], what="forge-cli")
+    proc = subprocess.run(cli + ["--temp", "0.8", "--top-k", "20", "--seed", "3", "--dtype", "bfloat16"], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len(proc.stdout.strip().splitlines()[0].split()) == 5
