@@ -89,10 +89,11 @@ class TidenexConfig:
             m = _section(layer, "mixer", where)
             if layer["type"] == "attention":
                 _heads(m, where)
-                rot = _section(m, "rot", where)
-                dims = optional(rot, "dims", int, m["dim"])
-                if dims % 2 or not 0 <= dims <= m["dim"] or not require(rot, "base", float) > 0.0:
-                    raise ConfigError(f"config.json: {where}rot.dims must be even and at most dim, rot.base positive")
+                if m.get("rot") is not None:          # a mixer without the key has no rotation
+                    rot = _section(m, "rot", where)
+                    dims = optional(rot, "dims", int, m["dim"])
+                    if dims % 2 or not 0 <= dims <= m["dim"] or not require(rot, "base", float) > 0.0:
+                        raise ConfigError(f"config.json: {where}rot.dims must be even and at most dim, rot.base positive")
                 require(m, "scale", float)
                 if not 0.0 <= require(m, "diff", float) < 1.0:
                     raise ConfigError(f"config.json: {where}diff must lie in [0, 1)")
@@ -101,8 +102,8 @@ class TidenexConfig:
                 _heads(left, where + "left: ")
                 _heads(right, where + "right: ", kv=False)
                 require(left, "scale", float)
-                require(m, "left_scale", float)
-                require(m, "right_scale", float)
+                optional(m, "left_scale", float, 1.0)
+                optional(m, "right_scale", float, 1.0)
                 if "q_temp" in left and left["q_temp"] is not None:
                     qt = _section(left, "q_temp", where + "left: ")
                     require(qt, "coef", float)
@@ -147,11 +148,11 @@ class TidenexConfig:
         m, W, eps = layer["mixer"], self.width, self.norm_eps
         if layer["type"] == "attention":
             dim = m["dim"]
+            rot = m.get("rot") or {"dims": 0, "base": 10000.0}
             return PartSpec("differential_attention", {
                 "hidden_size": W, "num_heads": m["heads"], "num_kv_heads": m.get("kv_heads", m["heads"]), "head_dim": dim,
                 "v_head_dim": m.get("vdim", dim), "scale": float(m["scale"]), "diff": float(m["diff"]), "eps": eps,
-                "position": PartSpec("rope_halves", {"head_dim": dim, "rotary_dims": m["rot"].get("dims", dim),
-                                                     "theta": float(m["rot"]["base"])})})
+                "position": PartSpec("rope_halves", {"head_dim": dim, "rotary_dims": rot.get("dims", dim), "theta": float(rot["base"])})})
         left, right = m["left"], m["right"]
         qt = left.get("q_temp") or {}
         return PartSpec("side_by_side", {"mixers": [
@@ -159,10 +160,10 @@ class TidenexConfig:
                 "hidden_size": W, "num_heads": left["heads"], "num_kv_heads": left.get("kv_heads", left["heads"]),
                 "head_dim": left["dim"], "v_head_dim": left.get("vdim", left["dim"]), "scale": float(left["scale"]), "eps": eps,
                 "temp_coef": float(qt.get("coef", 0.0)), "temp_every": float(qt.get("every", 0.0)),
-                "out_scale": float(m["left_scale"]), "prefix": "mix.left."}),
+                "out_scale": float(m.get("left_scale", 1.0)), "prefix": "mix.left."}),
             PartSpec("gated_write", {
                 "hidden_size": W, "num_heads": right["heads"], "head_dim": right["dim"], "v_head_dim": right.get("vdim", right["dim"]),
-                "eps": eps, "out_scale": float(m["right_scale"]), "prefix": "mix.right."})]})
+                "eps": eps, "out_scale": float(m.get("right_scale", 1.0)), "prefix": "mix.right."})]})
 
     def plan(self) -> ModelPlan:
         W = self.width

@@ -51,16 +51,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // M == 1 and nsplit == 1: out bf16 [T, H, E] (times out_scale).  Otherwise u fp32 [nsplit, T, H, M, E]: normalised with
 // nsplit == 1; with nsplit > 1 (steps of single tokens: a request's key tiles are dealt out to nsplit CTAs in runs) each run
 // leaves its sums as they are, beside the row's maximum (in units of log2 e) and sum in part_ml [nsplit, T, H, M, 2].
-template <int VC>
+template <int VC, bool SPLIT>
 __global__ void __launch_bounds__(kThreads)
 scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ u,
-                  __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
+                  __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml, int nsplit_given, int T, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
                   int max_pages, float scale, float out_scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
+    const int nsplit = SPLIT ? nsplit_given : 1;          // (a prompt's kernel is compiled without the dealing out)
     // the last tiles of a prompt see the most keys: they start first, so that the short ones fill the grid's tail
     const int tile = gridDim.x / nsplit - 1 - blockIdx.x / nsplit, sp = blockIdx.x % nsplit, c = blockIdx.y / M, mp = blockIdx.y % M, v0 = blockIdx.z * VC;
     const int t0 = tile_t0 ? tile_t0[tile] : tile;
@@ -280,9 +281,8 @@ scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows) return;
-    float wt[2][kMaxSplit];              // the weight of run s of map m (nsplit == 1: one)
-    for (int m = 0; m < M; ++m) {
-        if (nsplit == 1) { wt[m][0] = 1.0f; continue; }
+    float wt[2][kMaxSplit];              // the weight of run s of map m (not used with one run)
+    for (int m = 0; m < M && nsplit > 1; ++m) {
         float mx = -INFINITY, den = 0.f;
         for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, part_ml[(((size_t)s * rows + w) * M + m) * 2]);
         for (int s = 0; s < nsplit; ++s) {
@@ -296,6 +296,7 @@ scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
         for (int s = 0; s < nsplit; ++s) wt[m][s] *= inv;
     }
     auto value = [&](int m, int e) {
+        if (nsplit == 1) return u[((size_t)w * M + m) * E + e];
         float a = 0.f;
         for (int s = 0; s < nsplit; ++s) a = fmaf(wt[m][s], u[(((size_t)s * rows + w) * M + m) * E + e], a);
         return a;
@@ -304,31 +305,50 @@ scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
         for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn(value(0, e) * post);
         return;
     }
-    float ss = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float o = value(0, e) - lambda * value(1, e);
-        ss = fmaf(o, o, ss);
+    constexpr int kKeep = 8;             // heads of up to 256 values stay in registers between the two walks: u is read once
+    float ss = 0.f, kept[kKeep];
+    const bool keep = E <= 32 * kKeep;
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int e = lane + 32 * i;
+            kept[i] = e < E ? value(0, e) - lambda * value(1, e) : 0.f;
+            ss = fmaf(kept[i], kept[i], ss);
+        }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            const float o = value(0, e) - lambda * value(1, e);
+            ss = fmaf(o, o, ss);
+        }
     }
     ss = forge::warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)E + eps) * post;
-    for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn((value(0, e) - lambda * value(1, e)) * inv);
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E) out[(size_t)w * E + e] = __float2bfloat16_rn(kept[i] * inv);
+        }
+    } else {
+        for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn((value(0, e) - lambda * value(1, e)) * inv);
+    }
 }
 
-forge::PerDeviceFlag g_attr_done[3];
+forge::PerDeviceFlag g_attr_done[6];
 
-template <int VC>
+template <int VC, bool SPLIT>
 int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                   const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, const float* r1,
                   const float* r2, float* u, __nv_bfloat16* out, float* part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E,
                   int page_size, long long page_stride, int max_pages, float scale, float out_scale) {
-    bool& done = g_attr_done[which].current();
+    bool& done = g_attr_done[which + (SPLIT ? 3 : 0)].current();
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(scored_mma_kernel<VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
+        cudaError_t e = cudaFuncSetAttribute(scored_mma_kernel<VC, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
         if (e != cudaSuccess) return forge::check_launch("scored_attention_mma (shared memory)", e);
         done = true;
     }
     return forge::check_launch("scored_attention_mma",
-                               forge::launch(scored_mma_kernel<VC>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
+                               forge::launch(scored_mma_kernel<VC, SPLIT>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
                                              tn, r1, r2, u, out, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale,
                                              out_scale));
 }
@@ -371,9 +391,10 @@ extern "C" int forge_scored_attention_mma(const void* q, const void* cache, cons
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
     const float os = (M == 1 && nsplit == 1) ? out_scale : 1.0f;
     int rc;
-    if (VC == 64) rc = launch_scored<64>(0, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
-    else if (VC == 128) rc = launch_scored<128>(1, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
-    else rc = launch_scored<256>(2, grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os);
+#define FORGE_SCORED_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os
+    if (nsplit > 1) rc = VC == 64 ? launch_scored<64, true>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, true>(1, FORGE_SCORED_ARGS) : launch_scored<256, true>(2, FORGE_SCORED_ARGS);
+    else rc = VC == 64 ? launch_scored<64, false>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, false>(1, FORGE_SCORED_ARGS) : launch_scored<256, false>(2, FORGE_SCORED_ARGS);
+#undef FORGE_SCORED_ARGS
     if (rc != FORGE_OK || (M == 1 && nsplit == 1)) return rc;
     const unsigned blocks = (unsigned)(((size_t)T * H + 3) / 4);
     return forge::check_launch("scored_combine", forge::launch(scored_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, (const float*)u,

@@ -65,8 +65,9 @@ def differential_attention(h, w, m, eps):
     q = (h @ w["q"].t()).view(T, H * 2, D)
     k = (h @ w["k"].t()).view(T, G * 2, D)
     v = (h @ w["v"].t()).view(T, G, E)
-    q = rotate_halves(q, pos, m["rot"]["base"], m["rot"]["dims"]).view(T, H, 2, D)
-    k = rotate_halves(k, pos, m["rot"]["base"], m["rot"]["dims"]).view(T, G, 2, D)
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}          # a mixer without the key has no rotation
+    q = rotate_halves(q, pos, rot["base"], rot["dims"]).view(T, H, 2, D)
+    k = rotate_halves(k, pos, rot["base"], rot["dims"]).view(T, G, 2, D)
     lam = math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + m["diff"]
     rep = H // G
     out = torch.zeros(T, H, E, dtype=h.dtype)
@@ -126,7 +127,7 @@ def gated_linear_recurrence(h, w, m, eps, state=None):
 def parallel_mixer(h, w, m, eps):
     left = biased_attention(h, {k[5:]: v for k, v in w.items() if k.startswith("left.")}, m["left"], eps)
     right, _ = gated_linear_recurrence(h, {k[6:]: v for k, v in w.items() if k.startswith("right.")}, m["right"], eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 MIXERS = {"attention": differential_attention, "parallel": parallel_mixer}

@@ -61,7 +61,7 @@ def test_every_run_of_a_repeated_layer_keeps_a_cache_of_its_own():
     (lambda d: d["layers"][1]["mixer"]["rot"].update(dims=7), "rot.dims"),
     (lambda d: d["layers"][1]["mixer"].update(diff=1.0), "diff"),
     (lambda d: d["layers"][1]["mixer"].pop("scale"), "scale"),
-    (lambda d: d["layers"][0]["mixer"].pop("left_scale"), "left_scale"),
+    (lambda d: d["layers"][0]["mixer"].update(left_scale="big"), "left_scale"),
     (lambda d: d["layers"][0]["mixer"]["left"]["q_temp"].update(every=0), "q_temp"),
     (lambda d: d["layers"][0]["mlp"].update(kind="moe"), "mlp.kind"),
     (lambda d: d["loop"].update(stop=9), "loop"),
@@ -73,6 +73,17 @@ def test_refusals(change, message):
     change(d)
     with pytest.raises(ConfigError, match=message):
         config_from_dict(d)
+
+
+def test_what_config_does_not_mention_does_not_exist():
+    d = copy.deepcopy(TID["X"])
+    d["layers"][1]["mixer"].pop("rot")
+    d["layers"][0]["mixer"].pop("right_scale")
+    d["layers"][0]["mixer"]["left"].pop("q_temp")
+    p = config_from_dict(d).plan()
+    assert p.layers[1].mixer.params["position"].params["rotary_dims"] == 0
+    inner = p.layers[0].mixer.params["mixers"]
+    assert inner[1].params["out_scale"] == 1.0 and inner[0].params["out_scale"] == 1.3 and inner[0].params["temp_every"] == 0.0
 
 
 def test_to_dict_round_trip():
