@@ -8,7 +8,7 @@
 // goes out in bfloat16 at once; with two, each map leaves its normalised output in fp32 and a second kernel takes
 // a_1 - lambda a_2, divides by the root mean square and scales.  The distance term is taken off the scores in fp32 before
 // the softmax (with the fast base-2 logarithm; the 32-bit kernel of attention_scored.cu uses log1pf).  mma.sync m16n8k16 (the legacy tensor path): S = Q K^T with K rows as the column-major operand, O += P V with
-// V through ldmatrix.trans; the softmax weights are rounded to bfloat16 as the value product's operand, their sums are not.
+// V through ldmatrix.trans; a softmax weight is the value product's operand as two bfloat16 numbers (16 bits of mantissa).
 #include "common.cuh"
 #include "checks.cuh"
 
@@ -208,15 +208,14 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 row_m[h] = m_new;
             }
             float tsum[2] = {0.f, 0.f};
-            uint32_t pa[BN / 16][4];                                          // P as the A operand, 16 keys per k-step
 #pragma unroll
-            for (int nt = 0; nt < BN / 8; ++nt) {
-                const float p0 = ex2(sacc[nt][0] - base[0]), p1 = ex2(sacc[nt][1] - base[0]);
-                const float p2 = ex2(sacc[nt][2] - base[1]), p3 = ex2(sacc[nt][3] - base[1]);
-                tsum[0] += p0 + p1;
-                tsum[1] += p2 + p3;
-                pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
-                pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+            for (int nt = 0; nt < BN / 8; ++nt) {                             // the weights stay in sacc, in fp32
+                sacc[nt][0] = ex2(sacc[nt][0] - base[0]);
+                sacc[nt][1] = ex2(sacc[nt][1] - base[0]);
+                sacc[nt][2] = ex2(sacc[nt][2] - base[1]);
+                sacc[nt][3] = ex2(sacc[nt][3] - base[1]);
+                tsum[0] += sacc[nt][0] + sacc[nt][1];
+                tsum[1] += sacc[nt][2] + sacc[nt][3];
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -232,16 +231,30 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 oacc[i][2] *= alpha[1];
                 oacc[i][3] *= alpha[1];
             }
-            // O += P V
+            // O += P V.  A weight enters the product as two bfloat16 numbers, its rounding and what the rounding left over
+            // (16 bits of mantissa together): the weights are 32-bit numbers, and where the two maps' outputs nearly cancel a
+            // weight rounded to 8 bits would show.
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk) {
+                uint32_t pa[4], pl[4];                                        // P as the A operand, 16 keys: rounded, and the rest
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const float* pv = sacc[2 * kk + half];
+                    const __nv_bfloat162 h01 = __floats2bfloat162_rn(pv[0], pv[1]), h23 = __floats2bfloat162_rn(pv[2], pv[3]);
+                    pa[half * 2] = *reinterpret_cast<const uint32_t*>(&h01);
+                    pa[half * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                    pl[half * 2] = pack_bf16(pv[0] - __low2float(h01), pv[1] - __high2float(h01));
+                    pl[half * 2 + 1] = pack_bf16(pv[2] - __low2float(h23), pv[3] - __high2float(h23));
+                }
 #pragma unroll
                 for (int nt = 0; nt < VC / 8; nt += 2) {
                     if (nt >= ntw) break;                                 // (the same for the whole warp)
                     uint32_t b[4];      // keys kk*16 .. +15 (rows), columns cb + nt*8 .. +15: matrices (k lo, n lo), (k hi, n lo), (k lo, n hi), (k hi, n hi)
                     ldmatrix_x4_trans(b, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + cb + nt * 8 + (lane >> 4) * 8);
-                    mma_bf16(oacc[nt], pa[kk], b[0], b[1]);
-                    mma_bf16(oacc[nt + 1], pa[kk], b[2], b[3]);
+                    mma_bf16(oacc[nt], pl, b[0], b[1]);
+                    mma_bf16(oacc[nt + 1], pl, b[2], b[3]);
+                    mma_bf16(oacc[nt], pa, b[0], b[1]);
+                    mma_bf16(oacc[nt + 1], pa, b[2], b[3]);
                 }
             }
         }
