@@ -96,7 +96,7 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
                         const int32_t* __restrict__ tile_t0, const int32_t* __restrict__ tile_n, const float* __restrict__ r1,
                         const float* __restrict__ r2, TC* __restrict__ out, int H, int G, int M, int D, int E, int page_size,
                         long long page_stride, int max_pages, float scale, float lambda, float post, float eps, float out_scale,
-                        int TQ, int KT) {
+                        int TQ, int KT, long long out_ld) {
     extern __shared__ float smem[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -202,7 +202,7 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
     if (M == 1) {
         for (int i = tid; i < rows * E; i += kAttThreads) {
             const int e = i % E, row = i / E, r = row % R, tq = row / R;
-            out[((size_t)(t0 + tq) * H + g * R + r) * E + e] = forge::from_float<TC>(acc[i] / ls[row] * out_scale);
+            out[(size_t)(t0 + tq) * out_ld + (size_t)(g * R + r) * E + e] = forge::from_float<TC>(acc[i] / ls[row] * out_scale);
         }
         return;
     }
@@ -220,7 +220,7 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
         ss = forge::warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)E + eps) * post * out_scale;
         for (int e = lane; e < E; e += 32)
-            out[((size_t)(t0 + tq) * H + g * R + r) * E + e] = forge::from_float<TC>((a1[e] / l1 - lambda * (a2[e] / l2)) * inv);
+            out[(size_t)(t0 + tq) * out_ld + (size_t)(g * R + r) * E + e] = forge::from_float<TC>((a1[e] / l1 - lambda * (a2[e] / l2)) * inv);
     }
 }
 
@@ -262,13 +262,14 @@ extern "C" long long forge_scored_attention_smem(int H, int G, int M, int D, int
     return (long long)scored_smem_bytes(H / (G > 0 ? G : 1), M, D, E, TQ, KT);
 }
 
-// q [T, H*M*D] and out [T, H*E] in the cache's type.  tile_t0 / tile_n int32 [num_tiles] (both null: one token a tile).
+// q [T, H*M*D] and out (rows of out_ld elements, the heads' H*E values at their start) in the cache's type.  tile_t0 / tile_n int32 [num_tiles] (both null: one token a tile).
 // r1, r2 fp32 [H] or both null.  M = 2: lambda, post and eps of the combination of the two maps.
 extern "C" int forge_scored_attention(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                       const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* r1,
                                       const float* r2, void* out, int dtype, int num_tiles, int H, int G, int M, int D, int E,
                                       int page_size, long long page_stride, int max_pages, float scale, float lambda, float post,
-                                      float eps, float out_scale, int TQ, int KT, cudaStream_t stream) {
+                                      float eps, float out_scale, int TQ, int KT, long long out_ld, cudaStream_t stream) {
+    if (out_ld < (long long)H * E) return forge::fail(FORGE_ERR_ARG, "scored_attention: output rows of %lld are too short", out_ld);
     if (num_tiles < 0 || H <= 0 || G <= 0 || D <= 0 || E <= 0 || H % G != 0 || (M != 1 && M != 2) || page_size <= 0 || max_pages <= 0 ||
         TQ <= 0 || KT <= 0)
         return forge::fail(FORGE_ERR_ARG, "scored_attention: bad sizes tiles=%d H=%d G=%d M=%d D=%d E=%d page=%d TQ=%d KT=%d", num_tiles,
@@ -289,7 +290,7 @@ extern "C" int forge_scored_attention(const void* q, const void* cache, const in
         }
         e = forge::launch(scored_attention_kernel<TT>, dim3(num_tiles, G), dim3(kAttThreads), smem, stream, 1, (const TT*)q,
                           (const TT*)cache, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, (TT*)out, H, G, M, D, E, page_size,
-                          page_stride, max_pages, scale, lambda, post, eps, out_scale, TQ, KT);
+                          page_stride, max_pages, scale, lambda, post, eps, out_scale, TQ, KT, out_ld);
     });
     return forge::check_launch("scored_attention", e);
 }

@@ -57,7 +57,7 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ u,
                   __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml, int nsplit_given, int T, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
-                  int max_pages, float scale, float out_scale) {
+                  int max_pages, float scale, float out_scale, long long out_ld) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -276,7 +276,8 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
             const int col = v0 + cb + nt * 8 + (lane & 3) * 2;
             if (col >= E) continue;
             const float a = oacc[nt][2 * h] * inv[h], b = oacc[nt][2 * h + 1] * inv[h];
-            if (M == 1 && nsplit == 1) *reinterpret_cast<uint32_t*>(out + head_index * E + col) = pack_bf16(a * out_scale, b * out_scale);
+            if (M == 1 && nsplit == 1)
+                *reinterpret_cast<uint32_t*>(out + (size_t)(t0 + r / Gq) * out_ld + (size_t)(c * Gq + r % Gq) * E + col) = pack_bf16(a * out_scale, b * out_scale);
             else *reinterpret_cast<float2*>(u + (head_index * M + mp) * E + col) = make_float2(a, b);
         }
     }
@@ -287,13 +288,14 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
 // by its root mean square (eps inside the root) and multiplies by post; with one map the output is the map's, times post.
 // out bf16 [T, H, E].
 __global__ void __launch_bounds__(128)
-scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, __nv_bfloat16* __restrict__ out, int rows,
-                      int M, int E, float lambda, float post, float eps) {
+scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, __nv_bfloat16* __restrict__ out_base, int rows,
+                      int H, int M, int E, float lambda, float post, float eps, long long out_ld) {
     constexpr int kMaxSplit = 16;
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows) return;
+    __nv_bfloat16* orow = out_base + (size_t)(w / H) * out_ld + (size_t)(w % H) * E;      // where (token, head) w's values go
     float wt[2][kMaxSplit];              // the weight of run s of map m (not used with one run)
     for (int m = 0; m < M && nsplit > 1; ++m) {
         float mx = -INFINITY, den = 0.f;
@@ -315,7 +317,7 @@ scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
         return a;
     };
     if (M == 1) {
-        for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn(value(0, e) * post);
+        for (int e = lane; e < E; e += 32) orow[e] = __float2bfloat16_rn(value(0, e) * post);
         return;
     }
     constexpr int kKeep = 8;             // heads of up to 256 values stay in registers between the two walks: u is read once
@@ -340,10 +342,10 @@ scored_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
 #pragma unroll
         for (int i = 0; i < kKeep; ++i) {
             const int e = lane + 32 * i;
-            if (e < E) out[(size_t)w * E + e] = __float2bfloat16_rn(kept[i] * inv);
+            if (e < E) orow[e] = __float2bfloat16_rn(kept[i] * inv);
         }
     } else {
-        for (int e = lane; e < E; e += 32) out[(size_t)w * E + e] = __float2bfloat16_rn((value(0, e) - lambda * value(1, e)) * inv);
+        for (int e = lane; e < E; e += 32) orow[e] = __float2bfloat16_rn((value(0, e) - lambda * value(1, e)) * inv);
     }
 }
 
@@ -353,7 +355,7 @@ template <int VC, bool SPLIT>
 int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                   const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, const float* r1,
                   const float* r2, float* u, __nv_bfloat16* out, float* part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E,
-                  int page_size, long long page_stride, int max_pages, float scale, float out_scale) {
+                  int page_size, long long page_stride, int max_pages, float scale, float out_scale, long long out_ld) {
     bool& done = g_attr_done[which + (SPLIT ? 3 : 0)].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(scored_mma_kernel<VC, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
@@ -363,7 +365,7 @@ int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const 
     return forge::check_launch("scored_attention_mma",
                                forge::launch(scored_mma_kernel<VC, SPLIT>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
                                              tn, r1, r2, u, out, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale,
-                                             out_scale));
+                                             out_scale, out_ld));
 }
 
 }  // namespace
@@ -376,13 +378,15 @@ extern "C" int forge_scored_mma_supports(int H, int G, int M, int D, int E, int 
 }
 
 // q bf16 [T, H*M*D]; u fp32 [nsplit, T, H, M, E] (scratch; not needed with M == 1 and nsplit == 1); part_ml fp32
-// [nsplit, T, H, M, 2] (scratch, nsplit > 1: steps of single tokens only); out bf16 [T, H*E].  tile_t0 / tile_n: tiles of consecutive
+// [nsplit, T, H, M, 2] (scratch, nsplit > 1: steps of single tokens only); out bf16, rows of out_ld elements (even) with the
+// heads' H*E values at their start.  tile_t0 / tile_n: tiles of consecutive
 // tokens of one request with tile_n * (H/G) <= 64 (both null: one token per tile, num_tiles = T).  r1, r2 fp32 [H] or null.
 extern "C" int forge_scored_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* r1,
                                           const float* r2, float* u, float* part_ml, int nsplit, void* out, int T, int num_tiles, int H, int G, int M, int D, int E,
                                           int page_size, long long page_stride, int max_pages, float scale, float lambda, float post,
-                                          float eps, float out_scale, cudaStream_t stream) {
+                                          float eps, float out_scale, long long out_ld, cudaStream_t stream) {
+    if (out_ld < (long long)H * E || (out_ld & 1)) return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: output rows of %lld elements", out_ld);
     if (!forge_scored_mma_supports(H, G, M, D, E, page_size))
         return forge::fail(FORGE_ERR_UNSUPPORTED, "scored_attention_mma: H=%d G=%d M=%d D=%d E=%d", H, G, M, D, E);
     if (T < 0 || num_tiles < 0 || max_pages <= 0 || (tile_t0 == nullptr) != (tile_n == nullptr) || (r1 == nullptr) != (r2 == nullptr) ||
@@ -404,15 +408,15 @@ extern "C" int forge_scored_attention_mma(const void* q, const void* cache, cons
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
     const float os = (M == 1 && nsplit == 1) ? out_scale : 1.0f;
     int rc;
-#define FORGE_SCORED_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os
+#define FORGE_SCORED_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os, out_ld
     if (nsplit > 1) rc = VC == 64 ? launch_scored<64, true>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, true>(1, FORGE_SCORED_ARGS) : launch_scored<256, true>(2, FORGE_SCORED_ARGS);
     else rc = VC == 64 ? launch_scored<64, false>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, false>(1, FORGE_SCORED_ARGS) : launch_scored<256, false>(2, FORGE_SCORED_ARGS);
 #undef FORGE_SCORED_ARGS
     if (rc != FORGE_OK || (M == 1 && nsplit == 1)) return rc;
     const unsigned blocks = (unsigned)(((size_t)T * H + 3) / 4);
     return forge::check_launch("scored_combine", forge::launch(scored_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, (const float*)u,
-                                                               (const float*)part_ml, nsplit, ob, T * H, M, E, lambda,
-                                                               (M == 1 ? 1.0f : post) * out_scale, eps));
+                                                               (const float*)part_ml, nsplit, ob, T * H, H, M, E, lambda,
+                                                               (M == 1 ? 1.0f : post) * out_scale, eps, out_ld));
 }
 
 FORGE_DEFINE_CHECKS_ENTRY(attention_scored_mma)

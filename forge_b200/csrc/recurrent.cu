@@ -269,7 +269,7 @@ token_shift_kernel(const TA* __restrict__ h, const float* __restrict__ state, lo
 template <typename TA>
 __global__ void __launch_bounds__(128)
 head_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight, ScanInput g, TA* __restrict__ out, int rows,
-                   int N, int K, float eps, int act, float scale, int share_w) {
+                   int N, int K, float eps, int act, float scale, int share_w, long long out_ld) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -286,7 +286,7 @@ head_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight
             const float gv = g.p[(size_t)t * g.ld + head * K + c];
             gate = scale * (act == 1 ? gv * sigmoidf(gv) : sigmoidf(gv));
         }
-        out[(size_t)t * N * K + head * K + c] = forge::from_float<TA>(src[c] * inv * weight[share_w ? c : head * K + c] * gate);
+        out[(size_t)t * out_ld + head * K + c] = forge::from_float<TA>(src[c] * inv * weight[share_w ? c : head * K + c] * gate);
     }
 }
 
@@ -390,9 +390,11 @@ extern "C" int forge_token_shift(const void* h, const float* state, long long st
     return forge::check_launch("token_shift", e);
 }
 
-// o fp32 [T, N*K]; weight fp32 [N*K]; g fp32 rows of ld_g (the gate before its activation); out of type dtype [T, N*K].
+// o fp32 [T, N*K]; weight fp32 [N*K]; g fp32 rows of ld_g (the gate before its activation); out of type dtype, rows of out_ld
+// elements with the N*K values at their start.
 extern "C" int forge_head_finish(const float* o, const float* weight, const float* g, int ld_g, void* out, int dtype, int T, int N,
-                                 int K, float eps, int act, float scale, int share_w, cudaStream_t stream) {
+                                 int K, float eps, int act, float scale, int share_w, long long out_ld, cudaStream_t stream) {
+    if (out_ld < (long long)N * K) return forge::fail(FORGE_ERR_ARG, "head_finish: output rows of %lld are too short", out_ld);
     if (T < 0 || N <= 0 || K <= 0 || act < 0 || act > 2 || (act != 2 && !g)) return forge::fail(FORGE_ERR_ARG, "head_finish: bad sizes T=%d N=%d K=%d", T, N, K);
     if (T == 0) return FORGE_OK;
     if ((long long)T * N > 0x7fffffffLL / 2) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_finish: too many rows");
@@ -400,7 +402,7 @@ extern "C" int forge_head_finish(const float* o, const float* weight, const floa
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
         e = forge::launch(head_finish_kernel<TT>, dim3(blocks), dim3(128), 0, stream, 1, o, weight, ScanInput{g, ld_g}, (TT*)out, T, N, K,
-                          eps, act, scale, share_w));
+                          eps, act, scale, share_w, out_ld));
     return forge::check_launch("head_finish", e);
 }
 

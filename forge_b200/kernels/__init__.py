@@ -68,11 +68,11 @@ _SIGNATURES = {
         "forge_headmix_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _I, _P],
         "forge_scored_prepare": [_P, _I] + [_P] * 7 + [_I] * 8 + [_F, _F, _F, _I, _LL, _P],
-        "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _P],
+        "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _LL, _P],
         "forge_scored_mma_supports": [_I] * 6,
-        "forge_scored_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_P],
+        "forge_scored_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_LL, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-        "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _P],
+        "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _LL, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
     },
     "decode_layers": {
@@ -850,15 +850,29 @@ def scored_tile_tokens(H, G, M, D, E, single_tokens=False):
     raise KernelError(f"scored attention: {H // G} heads of {M}x{D}/{E} channels do not fit a CTA's shared memory")
 
 
+def _out_slice(out, n, T, dtype, device):
+    """(tensor, pointer, row stride in elements) of a kernel's output of n columns: a new [T, n] tensor, or, given
+    ``out`` = (matrix [T, >= col + n] of ``dtype``, first column), that slice of the matrix."""
+    if out is None:
+        t = new_tensor((T, n), dtype, device)
+        return t, t.data_ptr(), n
+    t, col = out
+    if t.dtype != dtype or t.shape[0] != T or t.shape[1] < col + n:
+        raise KernelError(f"output slice of {n} columns from {col} does not fit a {tuple(t.shape)} {t.dtype} matrix")
+    return t, _need(t, "out", dtype, 2) + t.element_size() * int(col), t.shape[1]
+
+
 def scored_prepare(proj, positions, slot_mapping, cache, H, G, M, D, E, page_size, act_dtype, inv_freq=None, q_norm=None,
-                   k_norm=None, eps=0.0, temp_coef=0.0, temp_every=0.0):
+                   k_norm=None, eps=0.0, temp_coef=0.0, temp_every=0.0, col=0):
     """proj fp32 [T, >= (H+G)*M*D + G*E] = [q | k | v] of a step's tokens: optionally an RMS norm over all of a token's query
     channels (weights ``q_norm`` fp32 [H*M*D]) and over all its key channels (``k_norm``), a rotation of the first
     2*len(inv_freq) channels of every map of D channels (channel i with i + half), a query temperature
     1 + temp_coef ln(floor((p+1)/temp_every) + 1); k and v go to ``slot_mapping`` in ``cache`` (None: no write); returns q
-    [T, H*M*D] in ``act_dtype``."""
+    [T, H*M*D] in ``act_dtype``.  ``col``: the first of the row's columns that are this mixer's."""
     lib = library("mixers")
     T, ld = proj.shape
+    if ld - col < (H + G) * M * D + G * E:
+        raise KernelError(f"scored_prepare: rows of {ld} from column {col} are too short")
     q = new_tensor((T, H * M * D), act_dtype, proj.device)
     if cache is not None and cache.dtype != act_dtype:
         raise KernelError("scored_prepare: cache and activation dtypes differ")
@@ -867,7 +881,7 @@ def scored_prepare(proj, positions, slot_mapping, cache, H, G, M, D, E, page_siz
     stride = _page_stride(cache) if cache is not None else G * page_size * (M * D + E)
     rot = 0 if inv_freq is None else 2 * inv_freq.numel()
     _check(lib, lib.forge_scored_prepare(
-        _need(proj, "proj", torch.float32, 2), ld, _need(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _need(proj, "proj", torch.float32, 2) + 4 * int(col), ld, _need(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
         _opt(inv_freq, "inv_freq", torch.float32) if rot else None, _opt(q_norm, "q_norm", torch.float32), _opt(k_norm, "k_norm", torch.float32),
         _need(q, "q", act_dtype), _opt(cache, "cache"), dtype_code(act_dtype), T, H * M, G * M, G, D, E, rot, float(eps), float(temp_coef),
         float(temp_every), page_size, stride, _stream()), "scored_prepare")
@@ -875,13 +889,14 @@ def scored_prepare(proj, positions, slot_mapping, cache, H, G, M, D, E, page_siz
 
 
 def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, scale, r1=None, r2=None, lam=0.0, post=1.0, eps=0.0,
-                     out_scale=1.0):
+                     out_scale=1.0, out=None):
     """Causal softmax attention of every token of the step over its request's pages, M maps per head (see
     csrc/attention_scored.cu): scores scale q.k - r1_h ln(1 + r2_h (i - j)); with M = 2 the maps' outputs are combined as
     a1 - lam a2, divided by their root mean square (``eps`` inside the root) and multiplied by ``post``.  Returns [T, H*E] in
-    q's type, times ``out_scale``."""
+    q's type, times ``out_scale``; ``out`` = (matrix, first column): written there instead (the matrix is returned)."""
     lib = library("mixers")
     T = q.shape[0]
+    out, out_ptr, out_ld = _out_slice(out, H * E, T, q.dtype, q.device)
     if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_scored_mma_supports.fn(H, G, M, D, E, page_size):
         # tensor cores: every (head, map) a one-pass attention of its own; two maps meet in a second small kernel
         t0, tn, tiles = headmix_plan(batch, max(1, 64 // (H // G)), q.device)
@@ -893,28 +908,26 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
             nsplit = max(1, min(8, -(-batch.max_context // 64), _sm_count(q.device) // max(1, ctas)))
         u = new_tensor((nsplit, T, H, M, E), torch.float32, q.device) if (M == 2 or nsplit > 1) else None
         part_ml = new_tensor((nsplit, T, H, M, 2), torch.float32, q.device) if nsplit > 1 else None
-        out = new_tensor((T, H * E), q.dtype, q.device)
         _check(lib, lib.forge_scored_attention_mma(
             _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
             _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
             _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _opt(u, "u", torch.float32),
-            _opt(part_ml, "part_ml", torch.float32), nsplit, _need(out, "out", torch.bfloat16), T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
-            float(scale), float(lam), float(post), float(eps), float(out_scale), _stream()), "scored_attention_mma")
+            _opt(part_ml, "part_ml", torch.float32), nsplit, out_ptr, T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
+            float(scale), float(lam), float(post), float(eps), float(out_scale), out_ld, _stream()), "scored_attention_mma")
         if M == 2 or nsplit > 1:
             count_launches(1)      # the kernel that puts the runs of key tiles, and the two maps, together
         return out
     single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
     TQ = scored_tile_tokens(H, G, M, D, E, single_tokens=single)
     t0, tn, tiles = headmix_plan(batch, TQ, q.device)
-    out = new_tensor((T, H * E), q.dtype, q.device)
     if cache.dtype != q.dtype:
         raise KernelError("scored_attention: q and cache dtypes differ")
     _check(lib, lib.forge_scored_attention(
         _need(q, "q", ndim=2), _need(cache, "cache"), _need(group_batch.block_table, "block_table", torch.int32, 2),
         _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
-        _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _need(out, "out", q.dtype),
+        _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), out_ptr,
         dtype_code(q.dtype), tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1], float(scale),
-        float(lam), float(post), float(eps), float(out_scale), TQ, SCORED_KEYS_PER_CHUNK, _stream()), "scored_attention")
+        float(lam), float(post), float(eps), float(out_scale), TQ, SCORED_KEYS_PER_CHUNK, out_ld, _stream()), "scored_attention")
     return out
 
 
@@ -971,20 +984,20 @@ def token_shift(h, state, prev_off, batch, mu):
 HEAD_GATES = {"sigmoid": 0, "silu": 1, "none": 2}
 
 
-def head_finish(o, weight, gate, N, K, eps, gate_activation, out_dtype, scale=1.0):
+def head_finish(o, weight, gate, N, K, eps, gate_activation, out_dtype, scale=1.0, out=None):
     """o fp32 [T, N*K]: every head divided by its root mean square (eps inside the root), times ``weight`` fp32 [N*K] (or [K],
     shared by the heads), times the activation of ``gate`` ((fp32 matrix, first column); None with "none"), times ``scale``;
-    [T, N*K] in ``out_dtype``."""
+    [T, N*K] in ``out_dtype``; ``out`` = (matrix, first column): written there instead (the matrix is returned)."""
     lib = library("mixers")
     T = o.shape[0]
-    out = new_tensor((T, N * K), out_dtype, o.device)
+    out, out_ptr, out_ld = _out_slice(out, N * K, T, out_dtype, o.device)
     gp, gl = _cols(*gate) if gate is not None else (None, 0)
     if weight.numel() not in (K, N * K):
         raise KernelError(f"head_finish: {weight.numel()} weights for {N} heads of {K}")
     share = 1 if (weight.numel() == K and N > 1) else 0
     _check(lib, lib.forge_head_finish(_need(o, "o", torch.float32, 2), _need(weight, "weight", torch.float32), gp, gl,
-                                      _need(out, "out", out_dtype), dtype_code(out_dtype), T, N, K, float(eps),
-                                      HEAD_GATES[gate_activation], float(scale), share, _stream()), "head_finish")
+                                      out_ptr, dtype_code(out_dtype), T, N, K, float(eps),
+                                      HEAD_GATES[gate_activation], float(scale), share, out_ld, _stream()), "head_finish")
     return out
 
 

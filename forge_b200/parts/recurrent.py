@@ -157,13 +157,23 @@ class GatedWriteMixer(Part):
     def cache_spec(self):
         return StateSpec((self.num_heads * self.head_dim * self.v_head_dim,), torch.float32)
 
-    def forward(self, x, batch, cache, residual):
+    def in_width(self):
+        return self.num_heads * (2 * self.head_dim + self.v_head_dim)
+
+    def out_width(self):
+        return self.num_heads * self.v_head_dim
+
+    def mix(self, p, col, batch, cache, out=None):
+        """p fp32 [T, >= col + in_width]: [q | f | v] from column ``col`` (q and f are overwritten); returns the normed heads
+        [T, N*V] (or writes them into ``out`` = (matrix, first column))."""
         N, K, V = self.num_heads, self.head_dim, self.v_head_dim
         NK = N * K
-        p = self.proj.forward(x)                                     # fp32 [T, 2*N*K + N*V]: q | f | v
-        o = kernels.state_scan("gated_write", (p, 0), None, (p, 2 * NK), (p, NK), self.f_bias, cache.state, batch, N, K,
+        o = kernels.state_scan("gated_write", (p, col), None, (p, col + 2 * NK), (p, col + NK), self.f_bias, cache.state, batch, N, K,
                                a0=self.lower, KV=V)
-        y = kernels.head_finish(o, self.norm, None, N, V, self.eps, "none", self.rt.dtype, scale=self.out_scale)
+        return kernels.head_finish(o, self.norm, None, N, V, self.eps, "none", self.rt.dtype, scale=self.out_scale, out=out)
+
+    def forward(self, x, batch, cache, residual):
+        y = self.mix(self.proj.forward(x), 0, batch, cache)          # the projection: fp32 [T, 2*N*K + N*V]
         self.o.forward(y, accumulate_into=residual)
 
 

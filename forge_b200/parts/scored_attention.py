@@ -44,6 +44,19 @@ class _ScoredAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.MAPS * self.head_dim, None, v_head_dim=self.v_head_dim)
 
+    # A mixer that runs beside others may share their input and output products: it says how many columns of the fused
+    # projection are its own and how many of the output product's input, and offers ``mix`` (everything between the two).
+    def in_width(self):
+        return (self.num_heads + self.num_kv_heads) * self.MAPS * self.head_dim + self.num_kv_heads * self.v_head_dim
+
+    def out_width(self):
+        return self.num_heads * self.v_head_dim
+
+    def forward(self, x, batch, cache, residual):
+        """x [T,W] normed input; cache: the layer's key/value pages; adds the output projection into residual."""
+        o = self.mix(self.proj.forward(x), 0, batch, cache)            # the projection: fp32 [T, in_width], biases added
+        self.o.forward(o, accumulate_into=residual)
+
     def _matrix_specs(self, bias):
         W, H, G, D, E, M = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.MAPS
         specs = {self._n("q"): TensorSpec((H * M * D, W)), self._n("k"): TensorSpec((G * M * D, W)), self._n("v"): TensorSpec((G * E, W)),
@@ -86,17 +99,17 @@ class DifferentialAttention(_ScoredAttention):
         v = {n: tensors[self._n(n)].to(torch.float64) for n in ("lq1", "lk1", "lq2", "lk2")}
         self.lam = math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum())) + self.diff
 
-    def forward(self, x, batch, cache, residual):
+    def mix(self, proj, col, batch, cache, out=None):
+        """proj fp32 [T, >= col + in_width]: [q | k | v] from column ``col``; returns the heads' outputs [T, H*E] (or writes them
+        into ``out`` = (matrix, first column))."""
         H, G, D, E = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
         g = batch.groups[cache.group]
-        proj = self.proj.forward(x)                                          # fp32 [T, (H+G)*2*D + G*E]
         freq = self.position.inv_freq
         q = kernels.scored_prepare(proj, batch.positions, g.slot_mapping if cache.writable else None,
                                    cache.kv if cache.writable else None, H, G, 2, D, E, cache.page_size, self.rt.dtype,
-                                   inv_freq=freq if freq.numel() else None)
-        o = kernels.scored_attention(q, cache.kv, g, batch, H, G, 2, D, E, cache.page_size, self.scale, lam=self.lam,
-                                     post=1.0 - self.diff, eps=self.eps, out_scale=self.out_scale)
-        self.o.forward(o, accumulate_into=residual)
+                                   inv_freq=freq if freq.numel() else None, col=col)
+        return kernels.scored_attention(q, cache.kv, g, batch, H, G, 2, D, E, cache.page_size, self.scale, lam=self.lam,
+                                        post=1.0 - self.diff, eps=self.eps, out_scale=self.out_scale, out=out)
 
 
 class DistanceBiasAttention(_ScoredAttention):
@@ -119,17 +132,17 @@ class DistanceBiasAttention(_ScoredAttention):
         self.q_norm, self.k_norm = self._vector_f32(tensors[self._n("q.norm")]), self._vector_f32(tensors[self._n("k.norm")])
         self.r1, self.r2 = self._vector_f32(tensors[self._n("r1")]), self._vector_f32(tensors[self._n("r2")])
 
-    def forward(self, x, batch, cache, residual):
+    def mix(self, proj, col, batch, cache, out=None):
+        """proj fp32 [T, >= col + in_width]: [q | k | v] from column ``col``, biases added; returns the heads' outputs
+        [T, H*E] (or writes them into ``out`` = (matrix, first column))."""
         H, G, D, E = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
         g = batch.groups[cache.group]
-        proj = self.proj.forward(x)                                          # fp32 [T, (H+G)*D + G*E], biases added
         q = kernels.scored_prepare(proj, batch.positions, g.slot_mapping if cache.writable else None,
                                    cache.kv if cache.writable else None, H, G, 1, D, E, cache.page_size, self.rt.dtype,
                                    q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, temp_coef=self.temp_coef,
-                                   temp_every=self.temp_every)
-        o = kernels.scored_attention(q, cache.kv, g, batch, H, G, 1, D, E, cache.page_size, self.scale, r1=self.r1, r2=self.r2,
-                                     out_scale=self.out_scale)
-        self.o.forward(o, accumulate_into=residual)
+                                   temp_every=self.temp_every, col=col)
+        return kernels.scored_attention(q, cache.kv, g, batch, H, G, 1, D, E, cache.page_size, self.scale, r1=self.r1, r2=self.r2,
+                                        out_scale=self.out_scale, out=out)
 
 
 register_part("mixer", "differential_attention", DifferentialAttention, replace=True)

@@ -175,8 +175,10 @@ def test_a_state_that_is_lost_shows(dtype):
 
 
 @pytest.mark.parametrize("dtype", DT)
-def test_side_by_side_mixers_in_a_layer(dtype):
-    """A whole pre-norm layer whose mixer is an attention beside a recurrence: pages and a state row behind one layer."""
+@pytest.mark.parametrize("rv", [4, 5])       # 5: an odd number of output columns in all, so the two mixers keep products of their own
+def test_side_by_side_mixers_in_a_layer(dtype, rv):
+    """A whole pre-norm layer whose mixer is an attention beside a recurrence: pages and a state row behind one layer, one
+    input product and one output product for both mixers."""
     from forge_b200.cache import CacheStorage
     from forge_b200.config import LayerSpec, PartSpec
     from forge_b200.engine import StepEntry, build_step_batch
@@ -186,13 +188,14 @@ def test_side_by_side_mixers_in_a_layer(dtype):
     mixer = PartSpec("side_by_side", {"mixers": [
         PartSpec("distance_attention", {"hidden_size": W, "num_heads": 4, "num_kv_heads": 2, "head_dim": 8, "v_head_dim": 12, "scale": 0.3,
                                         "eps": eps, "temp_coef": 0.4, "temp_every": 5.0, "out_scale": 0.6, "prefix": "mix.left."}),
-        PartSpec("gated_write", {"hidden_size": W, "num_heads": 3, "head_dim": 8, "v_head_dim": 4, "eps": eps, "out_scale": 1.7,
+        PartSpec("gated_write", {"hidden_size": W, "num_heads": 3, "head_dim": 8, "v_head_dim": rv, "eps": eps, "out_scale": 1.7,
                                  "prefix": "mix.right."})]})
     spec = LayerSpec(block="pre_norm", mixer=mixer, feed_forward=PartSpec("dense", {"hidden_size": W, "intermediate_size": 72}),
                      norms={"input": norm("norm1"), "post_mixer": norm("norm2")}, weight_prefix="", norm_prefixes={"input": "", "post_mixer": ""})
     block = build_block(spec, _rt(dtype))
     bt, _ = _bf16_weights(block, 0.25, seed=3)
     block.bind(bt)
+    assert (block.mixer.proj is not None) == (rv == 4)
     storage = CacheStorage([block.mixer.cache_spec()], [None], 8, 8, 1, dtype, torch.device(DEV))
     assert len(storage.layers[0].parts) == 2 and storage.layers[0].parts[0].kv is not None and storage.layers[0].parts[1].state is not None
     storage.manager.admit("r")
@@ -207,7 +210,7 @@ def test_side_by_side_mixers_in_a_layer(dtype):
     d = {k: v.double() for k, v in bt.items()}
     mw = {k.split("mix.", 1)[1]: v for k, v in d.items() if k.startswith("mix.")}
     m = {"left": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "scale": 0.3, "q_temp": {"coef": 0.4, "every": 5}},
-         "right": {"heads": 3, "dim": 8, "vdim": 4}, "left_scale": 0.6, "right_scale": 1.7}
+         "right": {"heads": 3, "dim": 8, "vdim": rv}, "left_scale": 0.6, "right_scale": 1.7}
     x = r0.double()
     x = x + PT.parallel_mixer(PT.layer_norm(x, d["norm1"], d["norm1.b"], eps), mw, m, eps)
     want = x + PT.dense_ff(PT.layer_norm(x, d["norm2"], d["norm2.b"], eps), d["mlp.up"], d["mlp.down"])
