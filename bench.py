@@ -471,11 +471,11 @@ def tidenex_shape(width, layers, heads, kv_heads, dim, ff, state_heads, state_di
     with two maps of ``dim`` channels and values of 2*dim, so that the projections are as large as the other decoder's) and one
     of an attention beside a gated linear recurrence, in turn; no repeated span, so that depth and weights are the other
     decoder's."""
-    att = {"type": "attention", "mixer": {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": dim, "vdim": 2 * dim, "diff": 0.6,
-                                          "rot": {"dims": dim // 2, "base": 50000.0}, "scale": dim ** -0.5}, "mlp": {"kind": "dense", "ff": ff}}
+    att = {"type": "attention", "mixer": {"heads": heads // 2, "kv_heads": max(1, kv_heads // 2), "dim": dim, "vdim": 2 * dim, "diff": 0.5,
+                                          "rot": {"dims": dim // 2, "base": 10000.0}, "scale": dim ** -0.5}, "mlp": {"kind": "dense", "ff": ff}}
     par = {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                                                  "q_temp": {"coef": 0.3, "every": 64}},
-                                         "right": {"heads": state_heads, "dim": state_dim, "vdim": state_dim}, "left_scale": 0.8, "right_scale": 1.1},
+                                                  "q_temp": {"coef": 0.25, "every": 128}},
+                                         "right": {"heads": state_heads, "dim": state_dim, "vdim": state_dim}, "left_scale": 0.9, "right_scale": 1.2},
            "mlp": {"kind": "dense", "ff": ff}}
     order = [att, att, par]
     return {"architecture": "Tidenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 8192,

@@ -41,7 +41,7 @@ TID = {
                      _with_mlp(_att(4, 2, 12, 12, 12, 1e6, 0.3, 0.5), 56)]},
     # widths at which the bfloat16 path takes the tensor-core products (every reduction a multiple of 8)
     "Z": {"architecture": "Tidenex", "vocab": 520, "width": 256, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 1, "times": 4},
-          "layers": [_with_mlp(_par(4, 2, 32, 64, 0.18, (0.3, 50), 4, 64, 32, 0.9, 1.2), 384),
+          "layers": [_with_mlp(_par(4, 2, 32, 64, 0.18, (0.35, 50), 4, 64, 32, 0.9, 1.2), 384),
                      _with_mlp(_att(8, 2, 32, 32, 16, 10000.0, 0.18, 0.4), 384)]},
 }
 SEEDS = {"X": 21, "Y": 22, "Z": 23}
