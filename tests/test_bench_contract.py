@@ -46,3 +46,22 @@ def test_the_design_option_keeps_to_one_gpu_and_counts_its_shapes():
     att = 256 * (8 * 32 + 2 * 32 + 2 * 32 + 8) + 256 * 8 * 32
     state = lambda n: 256 * 128 * n + 16 * (256 + 128)
     assert layers == 2 * att + state(5) + state(6) + 4 * 3 * 256 * 512 and head == 300 * 256
+
+
+def test_the_other_design_option_too():
+    rc, lines = _run("--design", "tidenex", "--gpus", "2")
+    assert rc == 2 and len(lines) == 1 and "single-GPU" in json.loads(lines[0])["error"]
+    sys.path.insert(0, ROOT)
+    import bench
+    import torch
+    from forge_b200.config import config_from_dict
+    from forge_b200.engine.model import Model
+    from forge_b200.parts import Runtime
+    z = dict(width=256, layers=3, heads=8, kv_heads=2, dim=32, ff=512, state_heads=4, state_dim=32, rank=16, window=64, vocab=300)
+    cfg = config_from_dict(bench.tidenex_shape(**z))
+    assert [l["type"] for l in cfg.layers] == ["attention", "attention", "parallel"] and cfg.loop is None
+    layers, head = bench.tidenex_matmul_params(cfg)
+    # counted from the configuration alone, the matrices are what the model's own tensor list holds (the head is the embedding)
+    specs = Model(cfg.plan(), Runtime(torch.device("cpu"), torch.bfloat16)).tensor_specs()
+    matrices = sum(s.shape[0] * s.shape[1] for n, s in specs.items() if len(s.shape) == 2 and s.required and n != "embed")
+    assert layers == matrices and head == 300 * 256
