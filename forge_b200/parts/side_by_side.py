@@ -42,8 +42,9 @@ class SideBySideMixers(Part):
         ms = self.mixers
         fusable = len(ms) > 1 and all(hasattr(m, "mix") and isinstance(getattr(m, "proj", None), Linear)
                                       and isinstance(getattr(m, "o", None), Linear) for m in ms)
-        # (an odd number of output columns would put a row of the shared buffer off the alignment of paired stores)
-        if not fusable or sum(m.out_width() for m in ms) % 2:
+        # (an odd number of output columns, in all or in front of a mixer, would put its rows of the shared buffer off the
+        # alignment of paired stores)
+        if not fusable or any(m.out_width() % 2 for m in ms):
             return
         dev = ms[0].proj.weight.device
 
